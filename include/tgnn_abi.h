@@ -1,0 +1,390 @@
+/*
+ * tgnn_abi.h -- C ABI of libturbo_gnn_b200.so
+ *
+ * One shared library, plain C signatures, no torch types.  It replaces the
+ * pybind11 module `turbo_gnn._C` of the reference (csrc/turbo_gnn.cpp:6-80)
+ * for the aggregation hot path.  Conventions that differ from the reference
+ * on purpose:
+ *
+ *   - The CALLER owns every byte of device memory: inputs, outputs and scratch.
+ *     Each op that needs scratch has a `*_workspace_bytes` query; the library
+ *     itself never allocates, frees, synchronises the device or calls exit().
+ *   - Every call names the device ordinal and the CUDA stream it runs on.
+ *   - Every call returns TGNN_OK (0) or a negative tgnn_status; the text of the
+ *     last failure on the calling thread is read with tgnn_last_error().  The
+ *     Python host turns a non-zero status into RuntimeError, which is what the
+ *     reference's autotuner relies on to skip invalid launch parameters
+ *     (turbo_gnn/_autotune.py:218-220).
+ *   - Rows of a CSR are scheduled in three tiers given by the caller as row-id
+ *     lists: `light` rows get one warp (or a sub-warp group) each, `heavy` rows
+ *     one CTA each, `hub` rows are split into chunks of `chunk_edges` edges
+ *     whose partial results are merged by a second pass.  light/heavy are the
+ *     reference's two buckets (turbo_gnn/graph.py:11-36); the hub tier is carved
+ *     out of the heavy bucket by the host.
+ *
+ * Feature matrices are row-major with the innermost dimension contiguous; the
+ * row stride (in elements) is free.  Vector (128-bit) access requires the base
+ * address and the row stride in bytes to be multiples of 16 and the feature
+ * count to be a multiple of 16/sizeof(element); the host pads or copies
+ * otherwise.
+ */
+#ifndef TGNN_ABI_H_
+#define TGNN_ABI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TGNN_ABI_VERSION 1
+
+typedef enum tgnn_status {
+    TGNN_OK = 0,
+    TGNN_ERR_INVALID_ARGUMENT = -1, /* bad dtype / shape / alignment / null pointer */
+    TGNN_ERR_UNSUPPORTED = -2,      /* valid request the kernels do not cover (e.g. head dim) */
+    TGNN_ERR_LAUNCH_PARAM = -3,     /* warps / chunk size outside the accepted set */
+    TGNN_ERR_WORKSPACE = -4,        /* scratch too small or missing */
+    TGNN_ERR_CUDA = -5              /* a CUDA runtime call failed; message has the code */
+} tgnn_status;
+
+typedef enum tgnn_dtype { TGNN_F32 = 0, TGNN_F16 = 1, TGNN_BF16 = 2 } tgnn_dtype;
+/* Unsigned index tensors are passed as their signed counterpart, like the
+ * reference does (csrc/common/traits.cuh:150-154). */
+typedef enum tgnn_itype { TGNN_I32 = 0, TGNN_I64 = 1 } tgnn_itype;
+
+typedef enum tgnn_reduce {
+    TGNN_REDUCE_MIN = 0,
+    TGNN_REDUCE_MAX = 1,
+    TGNN_REDUCE_SUM = 2,
+    TGNN_REDUCE_MEAN = 3
+} tgnn_reduce;
+
+/* Where a call runs. */
+typedef struct tgnn_exec {
+    int32_t device; /* CUDA device ordinal that owns every pointer of the call */
+    int32_t _pad;
+    void *stream;   /* cudaStream_t; NULL = legacy default stream */
+} tgnn_exec;
+
+/* One CSR (either direction).  Row = the node results are written for,
+ * column = the node features are gathered from. */
+typedef struct tgnn_csr {
+    const void *indptr;  /* [num_rows + 1], itype */
+    const void *indices; /* [num_edges], itype, values in [0, num_cols) */
+    int64_t num_rows;
+    int64_t num_cols;
+    int64_t num_edges;
+    int32_t itype; /* tgnn_itype, shared by indptr, indices and the row lists */
+    int32_t _pad;
+} tgnn_csr;
+
+/* Three-tier row schedule over one CSR.  Any tier may be empty.  Row ids are
+ * of the CSR's itype.  Hub row k (k-th entry of hub_rows) owns the chunks
+ * hub_part_ptr[k] .. hub_part_ptr[k+1]-1; chunk c covers the edges
+ * indptr[row] + (c - hub_part_ptr[k]) * chunk_edges up to chunk_edges more
+ * (clipped at the row end). chunk_hub[c] = k. */
+typedef struct tgnn_schedule {
+    const void *light_rows;
+    int64_t num_light;
+    const void *heavy_rows;
+    int64_t num_heavy;
+    const void *hub_rows;
+    int64_t num_hub;
+    const int32_t *hub_part_ptr; /* [num_hub + 1] */
+    const int32_t *chunk_hub;    /* [num_chunks] */
+    int64_t num_chunks;
+    int32_t chunk_edges;  /* edges per hub chunk, multiple of 32, 32..65536 */
+    int32_t light_warps;  /* warps per CTA in the light tier: 1,2,4,8 */
+    int32_t heavy_warps;  /* warps per CTA in the heavy and hub tiers: 1..16 */
+    int32_t _pad;
+} tgnn_schedule;
+
+/* Row-major matrix view; `cols` contiguous elements per row. */
+typedef struct tgnn_mat {
+    void *data;
+    int64_t rows;
+    int64_t cols;
+    int64_t row_stride; /* elements between consecutive rows, >= cols */
+    int32_t dtype;      /* tgnn_dtype */
+    int32_t _pad;
+} tgnn_mat;
+
+/* ---- library ------------------------------------------------------------ */
+
+/* Returns TGNN_ABI_VERSION of the loaded binary. */
+int32_t tgnn_abi_version(void);
+
+/* Copies the calling thread's last error text (NUL-terminated) into buf. */
+void tgnn_last_error(char *buf, size_t buf_len);
+
+/* ---- scratch ------------------------------------------------------------ */
+
+typedef enum tgnn_op {
+    TGNN_OP_REDUCE_MINMAX = 0,
+    TGNN_OP_WEIGHTED_SUM = 1, /* sum / mean / spmm, either direction */
+    TGNN_OP_GATV2_FWD = 2,
+    TGNN_OP_GATV2_BWD_DST = 3,
+    TGNN_OP_GATV2_BWD_SRC = 4,
+    TGNN_OP_GT_FWD = 5,
+    TGNN_OP_GT_BWD_DST = 6,
+    TGNN_OP_GT_BWD_SRC = 7
+} tgnn_op;
+
+/* Bytes of caller scratch `op` needs for a schedule with `num_chunks` hub
+ * chunks over rows of `feat_cols` elements of `dtype` (indices of `itype`).
+ * 0 when the schedule has no hub rows.  The scratch must be 256-byte aligned.  It replaces the
+ * reference's per-call allocations (`packed`, csrc/reduction/reduction_aggr.cu:548-550;
+ * `G`/`grad_a`, csrc/gatv2/gatv2_kernel.cu:322-327; `dK_f32`,
+ * csrc/gt/graph_transformer.cu:242). */
+size_t tgnn_workspace_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_chunks, int64_t feat_cols);
+
+/* ---- segment reductions -------------------------------------------------- */
+
+/* out[v,f] = reduce_{u in row v} x[u,f].
+ * MIN/MAX replace `reduction_aggr_forward_partitioned` (csrc/turbo_gnn.cpp:8-13,
+ * csrc/reduction/reduction_aggr_base.cu:42-101): an empty row gives 0 and
+ * arg -1; ties go to the lowest source id (csrc/reduction/reduction_aggr.cu:48-59);
+ * a NaN never wins.  SUM/MEAN replace the cuSPARSE route the reference takes for
+ * sum and mean (csrc/spmm/cusparse_spmm.cpp:268): fp32 accumulation, MEAN divides
+ * by max(degree, 1).  Rows that appear in no tier list are left untouched. */
+typedef struct tgnn_segment_reduce_args {
+    tgnn_exec exec;
+    tgnn_csr csr;
+    tgnn_schedule sched;
+    tgnn_mat x;   /* [csr.num_cols, F] */
+    tgnn_mat out; /* [csr.num_rows, F], dtype of x */
+    void *arg_idx; /* MIN/MAX: [num_rows, F] of csr.itype, contiguous, or NULL to skip; else ignored */
+    int32_t reduce; /* tgnn_reduce */
+    int32_t _pad;
+    void *workspace;
+    size_t workspace_bytes;
+} tgnn_segment_reduce_args;
+int32_t tgnn_segment_reduce_forward(const tgnn_segment_reduce_args *a);
+
+/* grad_x[arg_idx[v,f], f] += grad_out[v,f]; grad_x is zeroed first.  Replaces
+ * `reduction_aggr_backward` (csrc/turbo_gnn.cpp:15-18,
+ * csrc/reduction/reduction_aggr_base.cu:22-40, kernel reduction_aggr.cu:423-444). */
+typedef struct tgnn_segment_reduce_bwd_args {
+    tgnn_exec exec;
+    tgnn_mat grad_out;   /* [R, F] */
+    const void *arg_idx; /* [R, F] of itype, contiguous; negative = no winner */
+    tgnn_mat grad_x;     /* [num_src, F], dtype of grad_out */
+    int32_t itype;
+    int32_t _pad;
+} tgnn_segment_reduce_bwd_args;
+int32_t tgnn_segment_reduce_backward(const tgnn_segment_reduce_bwd_args *a);
+
+/* ---- weighted sum (g-SpMM) ------------------------------------------------ */
+
+typedef enum tgnn_norm { TGNN_NORM_NONE = 0, TGNN_NORM_RIGHT = 1, TGNN_NORM_LEFT = 2, TGNN_NORM_BOTH = 3 } tgnn_norm;
+
+/* Scale vectors for `norm` over a CSR whose rows are destinations:
+ *   row_scale[v] = 1 (none, left) | 1/max(in_deg v,1) (right) | 1/sqrt(max(in_deg v,1)) (both)
+ *   col_scale[u] = 1 (none, right)| 1/max(out_deg u,1) (left) | 1/sqrt(max(out_deg u,1)) (both)
+ * so that weight(u->v) = row_scale[v] * col_scale[u], the per-edge value of
+ * csrc/spmm/edge_norm_kernels.cu:26-60.  `col_count` is int32 scratch
+ * [num_cols] (zeroed by the call).  Replaces `compute_degrees`
+ * (csrc/turbo_gnn.cpp:76-79) and the weight pre-pass of `csr_SPMM_normalized`. */
+typedef struct tgnn_degree_norm_args {
+    tgnn_exec exec;
+    tgnn_csr csr;
+    int32_t norm;
+    int32_t _pad;
+    float *row_scale;   /* [num_rows] */
+    float *col_scale;   /* [num_cols] */
+    int32_t *col_count; /* [num_cols] scratch */
+} tgnn_degree_norm_args;
+int32_t tgnn_degree_norm(const tgnn_degree_norm_args *a);
+
+/* out[v,:] = row_scale[v] * sum_{e=(u->v)} edge_weight[e] * col_scale[u] * x[u,:]
+ * with fp32 accumulation; NULL scale / weight pointers mean 1.  The forward of
+ * `csr_SPMM_normalized` (csrc/turbo_gnn.cpp:50-54, csrc/spmm/cusparse_spmm.cpp:90-283)
+ * is this call on the forward CSR; its `do_transpose_a=True` backward is this
+ * call on the transposed CSR with the two scale vectors swapped. */
+typedef struct tgnn_spmm_args {
+    tgnn_exec exec;
+    tgnn_csr csr;
+    tgnn_schedule sched;
+    tgnn_mat x;   /* [csr.num_cols, F] */
+    tgnn_mat out; /* [csr.num_rows, F] */
+    const float *row_scale;
+    const float *col_scale;
+    const float *edge_weight; /* [num_edges] in this CSR's edge order */
+    void *workspace;
+    size_t workspace_bytes;
+} tgnn_spmm_args;
+int32_t tgnn_spmm(const tgnn_spmm_args *a);
+
+/* ---- attention: shared pieces -------------------------------------------- */
+
+/* Attention operands are [rows, heads*head_dim] matrices (a [N,H,D] tensor whose
+ * head stride is D).  head_dim must be one of 16, 32, 64, 128, 256 (the reference
+ * takes 32..256, csrc/gatv2/gatv2_kernel.cu:191; the host zero-pads other sizes).
+ * Score, softmax and accumulation run in fp32 for every element dtype. */
+
+/* dot[v,h] = sum_d a[v,h,d] * b[v,h,d], fp32 [rows, heads].  Gives
+ * Delta = <dO, O> of the graph-transformer backward (kernel K13,
+ * csrc/gt/gt_backward.cu:10-56) and G = <grad_out, out> of the GATv2 backward
+ * (equal to the first neighbour sweep of csrc/gatv2/gatv2_backward.cu:113-152). */
+typedef struct tgnn_head_dot_args {
+    tgnn_exec exec;
+    tgnn_mat a;
+    tgnn_mat b;
+    int32_t heads;
+    int32_t head_dim;
+    float *dot; /* [rows, heads] */
+} tgnn_head_dot_args;
+int32_t tgnn_head_dot(const tgnn_head_dot_args *a);
+
+/* ---- GATv2 ---------------------------------------------------------------- */
+
+/* e_ij = sum_d attn[h,d] * LeakyReLU(l[i,h,d] + r[j,h,d]); online softmax over
+ * the row; out[i] = sum_j alpha_ij r[j]; lse[i,h] = m + log s (-inf and a zero
+ * row for an empty row).  Replaces `gatv2_forward` (csrc/turbo_gnn.cpp:21-25,
+ * csrc/gatv2/gatv2_kernel.cu:124-231, kernel csrc/gatv2/gatv2_forward.cu:11-209). */
+typedef struct tgnn_gatv2_fwd_args {
+    tgnn_exec exec;
+    tgnn_csr csr;
+    tgnn_schedule sched;
+    tgnn_mat l;       /* [csr.num_rows, H*D] destination side */
+    tgnn_mat r;       /* [csr.num_cols, H*D] source side */
+    const void *attn; /* [H, D] contiguous, dtype of l */
+    int32_t heads;
+    int32_t head_dim;
+    float negative_slope;
+    int32_t _pad;
+    tgnn_mat out; /* [csr.num_rows, H*D] */
+    float *lse;   /* [csr.num_rows, H] */
+    void *workspace;
+    size_t workspace_bytes;
+} tgnn_gatv2_fwd_args;
+int32_t tgnn_gatv2_forward(const tgnn_gatv2_fwd_args *a);
+
+/* Destination-side half of `gatv2_backward` (csrc/turbo_gnn.cpp:27-33; kernel K7,
+ * csrc/gatv2/gatv2_backward.cu:10-229), over the forward CSR:
+ *   alpha = exp(e_ij - lse_i); ge = alpha (<gh_i, r_j> - G_i);
+ *   grad_l[i] = sum_j ge * LReLU'(z) * attn;  grad_attn[h,d] += sum_ij ge * LReLU(z).
+ * grad_attn_f32 is fp32 [H, D]; this call ADDS into it (zero it first); the sum
+ * over rows uses fp32 atomics, which replaces K9 (gatv2_backward.cu:380-440). */
+typedef struct tgnn_gatv2_bwd_dst_args {
+    tgnn_exec exec;
+    tgnn_csr csr;
+    tgnn_schedule sched;
+    tgnn_mat grad_out; /* [rows, H*D] */
+    tgnn_mat l;        /* [rows, H*D] */
+    tgnn_mat r;        /* [cols, H*D] */
+    const void *attn;
+    const float *lse; /* [rows, H] */
+    const float *G;   /* [rows, H] = <grad_out, out> */
+    int32_t heads;
+    int32_t head_dim;
+    float negative_slope;
+    int32_t _pad;
+    tgnn_mat grad_l;      /* [rows, H*D] */
+    float *grad_attn_f32; /* [H, D] */
+    void *workspace;
+    size_t workspace_bytes;
+} tgnn_gatv2_bwd_dst_args;
+int32_t tgnn_gatv2_backward_dst(const tgnn_gatv2_bwd_dst_args *a);
+
+/* Source-side half (kernel K8, csrc/gatv2/gatv2_backward.cu:234-378), over the
+ * transposed CSR (row = source j, column = destination i):
+ *   grad_r[j] = sum_i alpha_ij gh_i + ge_ij * LReLU'(z) * attn. */
+typedef struct tgnn_gatv2_bwd_src_args {
+    tgnn_exec exec;
+    tgnn_csr csr_t;
+    tgnn_schedule sched;
+    tgnn_mat grad_out; /* [cols of csr_t, H*D] destination side */
+    tgnn_mat l;        /* [cols of csr_t, H*D] */
+    tgnn_mat r;        /* [rows of csr_t, H*D] */
+    const void *attn;
+    const float *lse; /* [cols of csr_t, H] */
+    const float *G;   /* [cols of csr_t, H] */
+    int32_t heads;
+    int32_t head_dim;
+    float negative_slope;
+    int32_t _pad;
+    tgnn_mat grad_r; /* [rows of csr_t, H*D] */
+    void *workspace;
+    size_t workspace_bytes;
+} tgnn_gatv2_bwd_src_args;
+int32_t tgnn_gatv2_backward_src(const tgnn_gatv2_bwd_src_args *a);
+
+/* ---- graph transformer ---------------------------------------------------- */
+
+/* s_ij = scale * <q[j], k[i]> (query of the SOURCE, key of the DESTINATION,
+ * csrc/gt/gt_forward.cu:117-124); out[i] = sum_j softmax_j(s_ij) v[j]; lse.
+ * Replaces `gt_forward_csr_mh` (csrc/turbo_gnn.cpp:36-40,
+ * csrc/gt/graph_transformer.cu:9-114). */
+typedef struct tgnn_gt_fwd_args {
+    tgnn_exec exec;
+    tgnn_csr csr;
+    tgnn_schedule sched;
+    tgnn_mat q; /* [cols, H*D] */
+    tgnn_mat k; /* [rows, H*D] */
+    tgnn_mat v; /* [cols, H*D] */
+    int32_t heads;
+    int32_t head_dim;
+    float scale;
+    int32_t _pad;
+    tgnn_mat out; /* [rows, H*D] */
+    float *lse;   /* [rows, H] */
+    void *workspace;
+    size_t workspace_bytes;
+} tgnn_gt_fwd_args;
+int32_t tgnn_gt_forward(const tgnn_gt_fwd_args *a);
+
+/* Destination-side half of `gt_backward_csr_mh` (csrc/turbo_gnn.cpp:42-47,
+ * csrc/gt/graph_transformer.cu:116-334), over the forward CSR, without atomics:
+ *   dS_ij = alpha_ij (<dO_i, v_j> - Delta_i);  dk[i] = sum_j scale dS_ij q[j]
+ * (the reference adds this term with fp32 atomics, csrc/gt/gt_backward.cu:218). */
+typedef struct tgnn_gt_bwd_dst_args {
+    tgnn_exec exec;
+    tgnn_csr csr;
+    tgnn_schedule sched;
+    tgnn_mat q;     /* [cols, H*D] */
+    tgnn_mat k;     /* [rows, H*D] */
+    tgnn_mat v;     /* [cols, H*D] */
+    tgnn_mat d_out; /* [rows, H*D] */
+    const float *lse;   /* [rows, H] */
+    const float *delta; /* [rows, H] */
+    int32_t heads;
+    int32_t head_dim;
+    float scale;
+    int32_t _pad;
+    tgnn_mat dk; /* [rows, H*D] */
+    void *workspace;
+    size_t workspace_bytes;
+} tgnn_gt_bwd_dst_args;
+int32_t tgnn_gt_backward_dst(const tgnn_gt_bwd_dst_args *a);
+
+/* Source-side half (kernel K14, csrc/gt/gt_backward.cu:62-245), over the
+ * transposed CSR: dv[j] = sum_i alpha_ij dO_i;  dq[j] = sum_i scale dS_ij k[i]. */
+typedef struct tgnn_gt_bwd_src_args {
+    tgnn_exec exec;
+    tgnn_csr csr_t;
+    tgnn_schedule sched;
+    tgnn_mat q;     /* [rows of csr_t, H*D] */
+    tgnn_mat k;     /* [cols of csr_t, H*D] */
+    tgnn_mat v;     /* [rows of csr_t, H*D] */
+    tgnn_mat d_out; /* [cols of csr_t, H*D] */
+    const float *lse;   /* [cols of csr_t, H] */
+    const float *delta; /* [cols of csr_t, H] */
+    int32_t heads;
+    int32_t head_dim;
+    float scale;
+    int32_t _pad;
+    tgnn_mat dq; /* [rows of csr_t, H*D] */
+    tgnn_mat dv; /* [rows of csr_t, H*D] */
+    void *workspace;
+    size_t workspace_bytes;
+} tgnn_gt_bwd_src_args;
+int32_t tgnn_gt_backward_src(const tgnn_gt_bwd_src_args *a);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* TGNN_ABI_H_ */

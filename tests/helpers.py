@@ -1,0 +1,40 @@
+"""Shared test utilities: seeded random graphs and error measures."""
+
+from __future__ import annotations
+
+import torch
+
+from turbo_gnn_b200.graph import AdjacencyForwardBackwardWithNodeBuckets
+
+
+def random_edges(n: int, e: int, seed: int, hubs: int = 0, hub_degree: int = 0, self_loops: bool = False,
+                 symmetric: bool = False) -> torch.Tensor:
+    """Deduplicated [2, E] int64 COO; optional `hubs` destination nodes with about `hub_degree` in-edges."""
+    g = torch.Generator().manual_seed(seed)
+    src = torch.randint(0, n, (e,), generator=g)
+    dst = torch.randint(0, n, (e,), generator=g)
+    if hubs:
+        hsrc = torch.randint(0, n, (hubs * hub_degree,), generator=g)
+        hdst = torch.arange(hubs).repeat_interleave(hub_degree)
+        src, dst = torch.cat([src, hsrc]), torch.cat([dst, hdst])
+    ei = torch.stack([src, dst])
+    if symmetric:
+        ei = torch.cat([ei, ei.flip(0)], 1)
+    if self_loops:
+        loops = torch.arange(n)
+        ei = torch.cat([ei, torch.stack([loops, loops])], 1)
+    key = torch.unique(ei[0] * n + ei[1])
+    return torch.stack([key // n, key % n])
+
+
+def make_graph(ei: torch.Tensor, n: int, index_dtype=torch.int32, quantile=0.99, device="cuda", is_directed=None):
+    g = AdjacencyForwardBackwardWithNodeBuckets.from_edge_list(ei, n, quantile=quantile, index_dtype=index_dtype,
+                                                                is_directed=is_directed)
+    return g.to(device)
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    """max |got - want| divided by max |want| (tensor-level relative error)."""
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    denom = want.abs().max().item()
+    return (got - want).abs().max().item() / max(denom, 1e-30)

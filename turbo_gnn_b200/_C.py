@@ -1,0 +1,727 @@
+"""Python face of the C ABI with the call signatures of the reference's ``turbo_gnn._C``.
+
+The reference binds twelve functions with pybind11 (``csrc/turbo_gnn.cpp:6-80``);
+its ``_functions.py`` calls seven of them positionally.  This module offers the
+same names and argument orders, so code written against ``turbo_gnn._C`` runs
+unchanged, but each function only validates, allocates outputs/scratch through
+torch's caching allocator and forwards raw pointers to ``libturbo_gnn_b200.so``.
+Nothing here computes; without the shared library every call raises.
+
+Differences a caller can observe:
+  * sum and mean are first-class reductions (``reduce="sum"|"mean"``) instead of
+    a cuSPARSE detour;
+  * ``gatv2_backward`` takes an optional ``out=`` (the forward result), which
+    removes one neighbour sweep; without it the forward is recomputed;
+  * ``csr_SPMM_normalized(..., do_transpose_a=True)`` needs the transposed CSR,
+    which is built once per graph with torch ops and cached.
+"""
+
+from __future__ import annotations
+
+import weakref
+from collections import OrderedDict
+
+import torch
+import torch.nn.functional as F
+
+from . import _abi, _schedule
+
+_HEAD_DIMS = (16, 32, 64, 128, 256)
+
+# Tunables of the hub tier that the reference signatures have no slot for.
+# `configure_hub_tier` changes them process-wide (the autotuner does).
+_hub_cfg = {
+    "chunk_edges": _schedule.DEFAULT_CHUNK_EDGES,
+    "hub_min_degree": _schedule.DEFAULT_HUB_MIN_DEGREE,
+    "sort_by_degree": True,
+}
+
+
+def configure_hub_tier(chunk_edges: int | None = None, hub_min_degree: int | None = None,
+                       sort_by_degree: bool | None = None) -> dict:
+    """Set the hub-tier parameters used by later calls; returns the previous values."""
+    old = dict(_hub_cfg)
+    if chunk_edges is not None:
+        _hub_cfg["chunk_edges"] = int(chunk_edges)
+    if hub_min_degree is not None:
+        _hub_cfg["hub_min_degree"] = int(hub_min_degree)
+    if sort_by_degree is not None:
+        _hub_cfg["sort_by_degree"] = bool(sort_by_degree)
+    return old
+
+
+class hub_tier:
+    """Context manager: run the enclosed calls with the given hub-tier parameters."""
+
+    def __init__(self, chunk_edges=None, hub_min_degree=None, sort_by_degree=None):
+        self._new = (chunk_edges, hub_min_degree, sort_by_degree)
+        self._old = None
+
+    def __enter__(self):
+        self._old = configure_hub_tier(*self._new)
+        return self
+
+    def __exit__(self, *exc):
+        _hub_cfg.update(self._old)
+        return False
+
+
+def current_hub_config() -> dict:
+    return dict(_hub_cfg)
+
+
+def _sched(indptr, light, heavy):
+    return _schedule.get_schedule(indptr, light, heavy, _hub_cfg["chunk_edges"], _hub_cfg["hub_min_degree"],
+                                  _hub_cfg["sort_by_degree"])
+
+
+def _check_index_family(indptr, *others):
+    for t in others:
+        if t.dtype != indptr.dtype:
+            raise RuntimeError(f"index tensors must share a dtype: {t.dtype} vs {indptr.dtype}")
+        if not t.is_cuda:
+            raise RuntimeError("index tensors must be CUDA tensors")
+
+
+def _scratch(op: int, sched: _schedule.TierSchedule, feat: torch.Tensor, itype: torch.dtype, cols: int):
+    need = _abi.workspace_bytes(op, feat.dtype, itype, sched.num_chunks, cols) if sched.num_chunks else 0
+    if need == 0:
+        return None, 0
+    buf = torch.empty(need, dtype=torch.uint8, device=feat.device)
+    return buf, need
+
+
+def _chunk_elems(dt: torch.dtype) -> int:
+    return 4 if dt == torch.float32 else 8
+
+
+def _rows_ok(t: torch.Tensor) -> bool:
+    """True when `t` ([N,F] or [N,H,D]) can be read with 16-byte row accesses as is."""
+    esz = t.element_size()
+    if t.stride(-1) != 1 and t.shape[-1] > 1:
+        return False
+    if t.dim() == 3 and t.shape[1] > 1 and t.stride(1) != t.shape[2]:
+        return False
+    if t.data_ptr() % 16 != 0:
+        return False
+    return t.shape[0] <= 1 or (t.stride(0) * esz) % 16 == 0
+
+
+def _as_rows(t: torch.Tensor) -> torch.Tensor:
+    return t if _rows_ok(t) else t.contiguous()
+
+
+def _pad_cols(t: torch.Tensor, cols: int) -> torch.Tensor:
+    return t if t.shape[-1] == cols else F.pad(t, (0, cols - t.shape[-1]))
+
+
+def _round_up(v: int, m: int) -> int:
+    return (v + m - 1) // m * m
+
+
+# ---------------------------------------------------------------------------------------
+# segment reductions
+# ---------------------------------------------------------------------------------------
+
+
+def reduction_aggr_forward_partitioned(
+    edge_ptr,
+    edge_idx,
+    X,
+    light_nodes,
+    heavy_nodes,
+    max_degree,
+    warps_per_block=8,
+    edges_per_block_heavy_nodes=128,
+    use_2d_kernel=False,
+    features_per_block=32,
+    tiles_y=8,
+    reduce="min",
+    want_arg=True,
+):
+    """``[out, arg_idx]`` of the segment reduction over the forward CSR.
+
+    Signature of ``reduction_aggr_forward_partitioned`` (``csrc/turbo_gnn.cpp:8-13``).
+    How the reference's launch parameters map onto the three tiers: ``warps_per_block``
+    = warps per CTA in the light (warp-per-row) tier, clipped to 8;
+    ``edges_per_block_heavy_nodes`` = edges per hub chunk (rounded to a multiple of 32);
+    ``tiles_y`` = warps per CTA of the heavy tier when ``use_2d_kernel`` is set;
+    ``features_per_block`` is validated like the reference does and otherwise unused.
+    ``reduce`` also accepts "sum" and "mean" (then ``arg_idx`` is ``None``).
+    """
+    if reduce not in _abi.REDUCE:
+        raise RuntimeError(f"Unknown reduce: {reduce}")
+    if X.dim() != 2:
+        raise RuntimeError("X must be 2D")
+    if warps_per_block not in (1, 2, 4, 8, 16, 32, 64):
+        raise RuntimeError("Wrong int value")
+    if edges_per_block_heavy_nodes not in (32, 64, 128, 256, 512, 1024, 2048):
+        raise RuntimeError("Wrong int value")
+    if use_2d_kernel:
+        if not (0 < tiles_y <= 32) or tiles_y & (tiles_y - 1):
+            raise RuntimeError("tiles_y must be a power of 2 in range [1, 32]")
+        if not (0 < features_per_block <= 1024) or features_per_block * tiles_y > 1024:
+            raise RuntimeError("features_per_block * tiles_y must be <= 1024")
+    _check_index_family(edge_ptr, edge_idx, light_nodes, heavy_nodes)
+    n_rows = edge_ptr.numel() - 1
+    feat = X.shape[1]
+    minmax = reduce in ("min", "max")
+    cols = _round_up(max(feat, 1), _chunk_elems(X.dtype))
+    x_in = _as_rows(_pad_cols(X, cols))
+    out = torch.empty((n_rows, cols), dtype=X.dtype, device=X.device)
+    arg = None
+    if minmax and want_arg:
+        arg = torch.empty((n_rows, cols), dtype=edge_ptr.dtype, device=X.device)
+    if n_rows > 0 and feat > 0:
+        sched = _schedule.get_schedule(
+            edge_ptr, light_nodes, heavy_nodes, int(edges_per_block_heavy_nodes) * 16
+            if not use_2d_kernel else _hub_cfg["chunk_edges"], _hub_cfg["hub_min_degree"], _hub_cfg["sort_by_degree"]
+        )
+        op = _abi.OP_REDUCE_MINMAX if minmax else _abi.OP_WEIGHTED_SUM
+        ws, ws_bytes = _scratch(op, sched, x_in, edge_ptr.dtype, cols)
+        heavy_warps = int(tiles_y) if use_2d_kernel else 8
+        args = _abi.SegmentReduceArgs(
+            exec=_abi.exec_of(x_in),
+            csr=_abi.csr_of(edge_ptr, edge_idx, X.shape[0]),
+            sched=sched.to_struct(min(int(warps_per_block), 8), heavy_warps),
+            x=_abi.mat_of(x_in),
+            out=_abi.mat_of(out),
+            arg_idx=_abi.ptr(arg),
+            reduce=_abi.REDUCE[reduce],
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
+        )
+        _abi.call("tgnn_segment_reduce_forward", args)
+    if cols != feat:
+        out = out[:, :feat].contiguous()
+        arg = None if arg is None else arg[:, :feat].contiguous()
+    return [out, arg]
+
+
+def reduction_aggr_backward(grad_out, arg_idx, num_src_nodes, warps_per_block=8):
+    """grad_x of min/max: each grad_out element goes to its winner row (``csrc/turbo_gnn.cpp:15-18``)."""
+    if grad_out.dim() != 2:
+        raise RuntimeError("grad_out must be 2D")
+    if arg_idx.shape != grad_out.shape:
+        raise RuntimeError("arg_idx and grad_out shapes must match")
+    feat = grad_out.shape[1]
+    cols = _round_up(max(feat, 1), _chunk_elems(grad_out.dtype))
+    g_in = _as_rows(_pad_cols(grad_out, cols))
+    a_in = arg_idx.contiguous() if cols == feat else F.pad(arg_idx, (0, cols - feat), value=-1).contiguous()
+    grad_x = torch.empty((int(num_src_nodes), cols), dtype=grad_out.dtype, device=grad_out.device)
+    args = _abi.SegmentReduceBwdArgs(
+        exec=_abi.exec_of(g_in),
+        grad_out=_abi.mat_of(g_in),
+        arg_idx=_abi.ptr(a_in),
+        grad_x=_abi.mat_of(grad_x),
+        itype=_abi.itype_code(arg_idx.dtype),
+    )
+    _abi.call("tgnn_segment_reduce_backward", args)
+    return grad_x if cols == feat else grad_x[:, :feat].contiguous()
+
+
+# ---------------------------------------------------------------------------------------
+# weighted sum (g-SpMM)
+# ---------------------------------------------------------------------------------------
+
+_SPMM_QUANTILE = 0.99
+_SPMM_CACHE_SLOTS = 32
+
+
+class _SpmmGraph:
+    """Everything derived from one (indptr, indices) pair: tiers, transpose, norm scales."""
+
+    def __init__(self, indptr, indices, num_cols):
+        self.refs = (weakref.ref(indptr), weakref.ref(indices))
+        self.num_cols = num_cols
+        self.sched = None
+        self.transposed = None  # (t_indptr, t_indices, perm)
+        self.t_sched = None
+        self.scales = {}  # norm -> (row_scale, col_scale) of the forward direction
+
+    def alive(self, indptr, indices) -> bool:
+        return self.refs[0]() is indptr and self.refs[1]() is indices
+
+
+_spmm_graphs: "OrderedDict[tuple, _SpmmGraph]" = OrderedDict()
+
+
+def _spmm_graph(indptr, indices, num_cols, use_cache=True) -> _SpmmGraph:
+    key = (id(indptr), id(indices), num_cols)
+    g = _spmm_graphs.get(key) if use_cache else None
+    if g is None or not g.alive(indptr, indices):
+        g = _SpmmGraph(indptr, indices, num_cols)
+        if use_cache:
+            _spmm_graphs[key] = g
+            while len(_spmm_graphs) > _SPMM_CACHE_SLOTS:
+                _spmm_graphs.popitem(last=False)
+    return g
+
+
+def clear_graph_cache():
+    """Forget cached transposes, schedules and norm scales (``csrc/turbo_gnn.cpp:73``)."""
+    _spmm_graphs.clear()
+    _schedule.clear_schedule_cache()
+
+
+def _bucket(indptr):
+    from .graph import _bucket_nodes_by_degree, _row_degrees
+
+    return _bucket_nodes_by_degree(_row_degrees(indptr), _SPMM_QUANTILE, index_dtype=indptr.dtype)
+
+
+def transpose_csr(indptr: torch.Tensor, indices: torch.Tensor, num_cols: int):
+    """CSR of the transposed matrix, entries ordered by (row, column); also the edge permutation.
+
+    ``perm[k]`` is the position in the input CSR of the k-th edge of the result.
+    """
+    n_rows = indptr.numel() - 1
+    sp = indptr.view(torch.int32) if indptr.dtype == torch.uint32 else indptr
+    si = indices.view(torch.int32) if indices.dtype == torch.uint32 else indices
+    deg = (sp[1:] - sp[:-1]).long()
+    row_of_edge = torch.repeat_interleave(torch.arange(n_rows, device=indptr.device), deg,
+                                          output_size=indices.numel())
+    key = si.long() * max(n_rows, 1) + row_of_edge
+    perm = torch.argsort(key)
+    t_indices = row_of_edge[perm].to(indices.dtype)
+    counts = torch.bincount(si.long(), minlength=num_cols)
+    t_indptr = torch.zeros(num_cols + 1, dtype=torch.long, device=indptr.device)
+    torch.cumsum(counts, 0, out=t_indptr[1:])
+    return t_indptr.to(indptr.dtype), t_indices, perm
+
+
+def _norm_scales(g: _SpmmGraph, indptr, indices, norm: str):
+    hit = g.scales.get(norm)
+    if hit is not None:
+        return hit
+    n_rows = indptr.numel() - 1
+    dev = indptr.device
+    row_scale = torch.empty(n_rows, dtype=torch.float32, device=dev)
+    col_scale = torch.empty(g.num_cols, dtype=torch.float32, device=dev)
+    col_count = torch.empty(g.num_cols, dtype=torch.int32, device=dev)
+    args = _abi.DegreeNormArgs(
+        exec=_abi.exec_of(indptr),
+        csr=_abi.csr_of(indptr, indices, g.num_cols),
+        norm=_abi.NORM[norm],
+        row_scale=_abi.ptr(row_scale),
+        col_scale=_abi.ptr(col_scale),
+        col_count=_abi.ptr(col_count),
+    )
+    _abi.call("tgnn_degree_norm", args)
+    g.scales[norm] = (row_scale, col_scale)
+    return g.scales[norm]
+
+
+def csr_SPMM_normalized(
+    indptr,
+    indices,
+    features,
+    edge_weights,
+    norm="none",
+    algorithm=-1,
+    use_cache=True,
+    do_transpose_a=False,
+    block_dim=256,
+):
+    """``out = norm(A) @ features`` (or ``norm(A)^T @ features``), signature of ``csrc/turbo_gnn.cpp:50-54``.
+
+    ``algorithm`` and ``block_dim`` selected cuSPARSE variants in the reference and are
+    accepted and ignored.  ``edge_weights`` with zero elements means all ones.
+    """
+    if norm not in _abi.NORM:
+        raise RuntimeError(f"unknown norm '{norm}'")
+    if features.dim() != 2:
+        raise RuntimeError("features must be 2D")
+    _check_index_family(indptr, indices)
+    n_rows = indptr.numel() - 1
+    num_cols = features.shape[0] if not do_transpose_a else None
+    if do_transpose_a:
+        # A is [n_rows x num_cols]; the reference only handles square adjacency here.
+        num_cols = n_rows if features.shape[0] == n_rows else None
+        if num_cols is None:
+            raise RuntimeError("do_transpose_a expects features with one row per CSR row")
+    g = _spmm_graph(indptr, indices, num_cols, use_cache)
+    feat = features.shape[1]
+    cols = _round_up(max(feat, 1), _chunk_elems(features.dtype))
+    x_in = _as_rows(_pad_cols(features, cols))
+    has_w = edge_weights is not None and edge_weights.numel() > 0
+    row_scale = col_scale = None
+    if norm != "none":
+        row_scale, col_scale = _norm_scales(g, indptr, indices, norm)
+    if not do_transpose_a:
+        if g.sched is None:
+            light, heavy = _bucket(indptr)
+            g.sched = _schedule.split_tiers(indptr, light, heavy, _hub_cfg["chunk_edges"],
+                                            _hub_cfg["hub_min_degree"], _hub_cfg["sort_by_degree"])
+        run_ptr, run_idx, sched, out_rows, src_rows = indptr, indices, g.sched, n_rows, g.num_cols
+        w = edge_weights.float().contiguous() if has_w else None
+        rs, cs = row_scale, col_scale
+    else:
+        if g.transposed is None:
+            g.transposed = transpose_csr(indptr, indices, g.num_cols)
+        t_ptr, t_idx, perm = g.transposed
+        if g.t_sched is None:
+            light, heavy = _bucket(t_ptr)
+            g.t_sched = _schedule.split_tiers(t_ptr, light, heavy, _hub_cfg["chunk_edges"],
+                                              _hub_cfg["hub_min_degree"], _hub_cfg["sort_by_degree"])
+        run_ptr, run_idx, sched, out_rows, src_rows = t_ptr, t_idx, g.t_sched, g.num_cols, n_rows
+        w = edge_weights.float()[perm].contiguous() if has_w else None
+        rs, cs = col_scale, row_scale  # roles swap under transposition
+    out = torch.empty((out_rows, cols), dtype=features.dtype, device=features.device)
+    if out_rows > 0:
+        ws, ws_bytes = _scratch(_abi.OP_WEIGHTED_SUM, sched, x_in, indptr.dtype, cols)
+        args = _abi.SpmmArgs(
+            exec=_abi.exec_of(x_in),
+            csr=_abi.csr_of(run_ptr, run_idx, src_rows),
+            sched=sched.to_struct(8, 8),
+            x=_abi.mat_of(x_in),
+            out=_abi.mat_of(out),
+            row_scale=_abi.ptr(rs),
+            col_scale=_abi.ptr(cs),
+            edge_weight=_abi.ptr(w),
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
+        )
+        _abi.call("tgnn_spmm", args)
+    return out if cols == feat else out[:, :feat].contiguous()
+
+
+def csr_SPMM(indptr, indices, features, algorithm=-1, use_cache=True, do_transpose_a=False, block_dim=256):
+    """Unnormalised SpMM (``csrc/turbo_gnn.cpp:56-60``)."""
+    empty = torch.empty(0, dtype=torch.float32, device=features.device)
+    return csr_SPMM_normalized(indptr, indices, features, empty, "none", algorithm, use_cache, do_transpose_a, block_dim)
+
+
+def find_best_algorithm_normalized(indptr, indices, features, edge_weights, norm="none", block_dim=256):
+    """The reference times cuSPARSE algorithm ids here (``csrc/turbo_gnn.cpp:62-66``); there is one kernel now."""
+    csr_SPMM_normalized(indptr, indices, features, edge_weights, norm)
+    return 0
+
+
+def find_best_algorithm(indptr, indices, features, block_dim=256):
+    csr_SPMM(indptr, indices, features)
+    return 0
+
+
+def compute_degrees(indptr, indices, in_degrees, out_degrees, block_dim=256):
+    """Fill ``in_degrees`` (row lengths) and ``out_degrees`` (column counts) (``csrc/turbo_gnn.cpp:76-79``)."""
+    num_cols = out_degrees.numel()
+    n_rows = indptr.numel() - 1
+    dev = indptr.device
+    row_scale = torch.empty(n_rows, dtype=torch.float32, device=dev)
+    col_scale = torch.empty(num_cols, dtype=torch.float32, device=dev)
+    col_count = torch.empty(num_cols, dtype=torch.int32, device=dev)
+    args = _abi.DegreeNormArgs(
+        exec=_abi.exec_of(indptr),
+        csr=_abi.csr_of(indptr, indices, num_cols),
+        norm=_abi.NORM["left"],
+        row_scale=_abi.ptr(row_scale),
+        col_scale=_abi.ptr(col_scale),
+        col_count=_abi.ptr(col_count),
+    )
+    _abi.call("tgnn_degree_norm", args)
+    out_degrees.copy_(col_count)
+    sp = indptr.view(torch.int32) if indptr.dtype == torch.uint32 else indptr
+    in_degrees.copy_(sp[1:] - sp[:-1])
+
+
+# ---------------------------------------------------------------------------------------
+# attention: shared host logic
+# ---------------------------------------------------------------------------------------
+
+
+def _padded_head_dim(d: int) -> int:
+    for cand in _HEAD_DIMS:
+        if d <= cand:
+            return cand
+    raise RuntimeError(f"head dimension {d} is above the supported maximum of {_HEAD_DIMS[-1]}")
+
+
+def _head_rows(t: torch.Tensor, d_pad: int) -> torch.Tensor:
+    """[N, H, D] -> tensor the kernels can read: head dim zero-padded to d_pad, rows 16-byte addressable."""
+    if t.dim() != 3:
+        raise RuntimeError(f"expected [N, H, D], got {tuple(t.shape)}")
+    if t.shape[2] != d_pad:
+        t = F.pad(t, (0, d_pad - t.shape[2]))
+    return _as_rows(t)
+
+
+def _clamp_light(w: int) -> int:
+    if w not in (1, 2, 4):
+        raise RuntimeError("Wrong int value")
+    return w
+
+
+def _clamp_heavy(w: int) -> int:
+    if w not in (8, 16, 32):
+        raise RuntimeError("Wrong int value")
+    return min(w, 16)
+
+
+def _check_attention_inputs(*tensors):
+    first = tensors[0]
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("inputs must be CUDA tensors")
+        if t.dtype != first.dtype:
+            raise RuntimeError("attention operands must share a dtype")
+    if first.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise RuntimeError("attention operands must be float32/float16/bfloat16")
+
+
+def _head_dot(a: torch.Tensor, b: torch.Tensor, heads: int, head_dim: int) -> torch.Tensor:
+    dot = torch.empty((a.shape[0], heads), dtype=torch.float32, device=a.device)
+    args = _abi.HeadDotArgs(exec=_abi.exec_of(a), a=_abi.mat_of(a), b=_abi.mat_of(b), heads=heads,
+                            head_dim=head_dim, dot=_abi.ptr(dot))
+    _abi.call("tgnn_head_dot", args)
+    return dot
+
+
+def _default_buckets(indptr):
+    return _bucket(indptr)
+
+
+# ---------------------------------------------------------------------------------------
+# GATv2
+# ---------------------------------------------------------------------------------------
+
+
+def gatv2_forward(l, r, row_ptr, col_idx, attn_vec, negative_slope, light_nodes, heavy_nodes,
+                  light_warps_per_block=1, heavy_warps_per_block=8):
+    """``[h_out [N,H,D], logsumexp [N,H] fp32]`` (``csrc/turbo_gnn.cpp:21-25``).
+
+    ``l`` is the destination-side and ``r`` the source-side projection.  Head dims other than
+    16/32/64/128/256 are zero-padded (features and attention vector), which leaves scores and
+    outputs unchanged.
+    """
+    _check_attention_inputs(l, r, attn_vec)
+    _check_index_family(row_ptr, col_idx, light_nodes, heavy_nodes)
+    n_rows, heads, d = l.shape
+    if attn_vec.shape != (heads, d) or r.shape[1:] != (heads, d):
+        raise RuntimeError("l, r must be [N, H, D] and attn_vec [H, D]")
+    lw, hw = _clamp_light(light_warps_per_block), _clamp_heavy(heavy_warps_per_block)
+    dp = _padded_head_dim(d)
+    l_in, r_in = _head_rows(l, dp), _head_rows(r, dp)
+    a_in = _pad_cols(attn_vec, dp).contiguous()
+    out = torch.empty((n_rows, heads, dp), dtype=l.dtype, device=l.device)
+    lse = torch.empty((n_rows, heads), dtype=torch.float32, device=l.device)
+    if n_rows > 0:
+        sched = _sched(row_ptr, light_nodes, heavy_nodes)
+        ws, ws_bytes = _scratch(_abi.OP_GATV2_FWD, sched, l_in, row_ptr.dtype, heads * dp)
+        args = _abi.Gatv2FwdArgs(
+            exec=_abi.exec_of(l_in),
+            csr=_abi.csr_of(row_ptr, col_idx, r.shape[0]),
+            sched=sched.to_struct(lw, hw),
+            l=_abi.mat_of(l_in),
+            r=_abi.mat_of(r_in),
+            attn=_abi.ptr(a_in),
+            heads=heads,
+            head_dim=dp,
+            negative_slope=float(negative_slope),
+            out=_abi.mat_of(out),
+            lse=_abi.ptr(lse),
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
+        )
+        _abi.call("tgnn_gatv2_forward", args)
+    if dp != d:
+        out = out[..., :d].contiguous()
+    return [out, lse]
+
+
+def gatv2_backward(grad_h, l, r, row_ptr, col_idx, row_ptr_T, col_idx_T, attn_vec, logsumexp, negative_slope,
+                   grad_A_reduce_row_chunk_size, fwd_light_nodes, fwd_heavy_nodes, bwd_light_nodes, bwd_heavy_nodes,
+                   light_warps_per_block=1, heavy_warps_per_block=8, is_directed=True, out=None):
+    """``[grad_l, grad_r, grad_attn]`` (``csrc/turbo_gnn.cpp:27-33``).
+
+    Two passes: destination side over the forward CSR (grad_l, grad_attn), source side over the
+    transposed CSR (grad_r).  ``is_directed=False`` means the caller aliased the transposed CSR to
+    the forward one; the same two passes run on it.  ``grad_A_reduce_row_chunk_size`` belonged to a
+    separate reduction kernel of the reference and is validated only.
+    """
+    if grad_A_reduce_row_chunk_size not in (32, 64, 128, 256, 512, 1024, 2048):
+        raise RuntimeError("Wrong int value")
+    _check_attention_inputs(l, r, attn_vec, grad_h)
+    _check_index_family(row_ptr, col_idx, row_ptr_T, col_idx_T, fwd_light_nodes, fwd_heavy_nodes, bwd_light_nodes,
+                        bwd_heavy_nodes)
+    n_rows, heads, d = l.shape
+    n_src = r.shape[0]
+    lw, hw = _clamp_light(light_warps_per_block), _clamp_heavy(heavy_warps_per_block)
+    dp = _padded_head_dim(d)
+    if out is None:
+        out = gatv2_forward(l, r, row_ptr, col_idx, attn_vec, negative_slope, fwd_light_nodes, fwd_heavy_nodes)[0]
+    l_in, r_in = _head_rows(l, dp), _head_rows(r, dp)
+    g_in, o_in = _head_rows(grad_h.reshape(n_rows, heads, d), dp), _head_rows(out.reshape(n_rows, heads, d), dp)
+    a_in = _pad_cols(attn_vec, dp).contiguous()
+    lse = logsumexp.contiguous()
+    grad_l = torch.empty((n_rows, heads, dp), dtype=l.dtype, device=l.device)
+    grad_r = torch.empty((n_src, heads, dp), dtype=l.dtype, device=l.device)
+    grad_a32 = torch.zeros((heads, dp), dtype=torch.float32, device=l.device)
+    if n_rows > 0:
+        G = _head_dot(g_in, o_in, heads, dp)
+        ex = _abi.exec_of(l_in)
+        cols = heads * dp
+        f_sched = _sched(row_ptr, fwd_light_nodes, fwd_heavy_nodes)
+        ws, ws_bytes = _scratch(_abi.OP_GATV2_BWD_DST, f_sched, l_in, row_ptr.dtype, cols)
+        dst_args = _abi.Gatv2BwdDstArgs(
+            exec=ex,
+            csr=_abi.csr_of(row_ptr, col_idx, n_src),
+            sched=f_sched.to_struct(lw, hw),
+            grad_out=_abi.mat_of(g_in),
+            l=_abi.mat_of(l_in),
+            r=_abi.mat_of(r_in),
+            attn=_abi.ptr(a_in),
+            lse=_abi.ptr(lse),
+            G=_abi.ptr(G),
+            heads=heads,
+            head_dim=dp,
+            negative_slope=float(negative_slope),
+            grad_l=_abi.mat_of(grad_l),
+            grad_attn_f32=_abi.ptr(grad_a32),
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
+        )
+        _abi.call("tgnn_gatv2_backward_dst", dst_args)
+        b_sched = _sched(row_ptr_T, bwd_light_nodes, bwd_heavy_nodes)
+        ws2, ws2_bytes = _scratch(_abi.OP_GATV2_BWD_SRC, b_sched, l_in, row_ptr.dtype, cols)
+        src_args = _abi.Gatv2BwdSrcArgs(
+            exec=ex,
+            csr_t=_abi.csr_of(row_ptr_T, col_idx_T, n_rows),
+            sched=b_sched.to_struct(lw, hw),
+            grad_out=_abi.mat_of(g_in),
+            l=_abi.mat_of(l_in),
+            r=_abi.mat_of(r_in),
+            attn=_abi.ptr(a_in),
+            lse=_abi.ptr(lse),
+            G=_abi.ptr(G),
+            heads=heads,
+            head_dim=dp,
+            negative_slope=float(negative_slope),
+            grad_r=_abi.mat_of(grad_r),
+            workspace=_abi.ptr(ws2),
+            workspace_bytes=ws2_bytes,
+        )
+        _abi.call("tgnn_gatv2_backward_src", src_args)
+    else:
+        grad_r.zero_()
+    grad_a = grad_a32.to(attn_vec.dtype)
+    if dp != d:
+        grad_l, grad_r, grad_a = grad_l[..., :d].contiguous(), grad_r[..., :d].contiguous(), grad_a[:, :d].contiguous()
+    return [grad_l, grad_r, grad_a]
+
+
+# ---------------------------------------------------------------------------------------
+# graph transformer
+# ---------------------------------------------------------------------------------------
+
+
+def gt_forward_csr_mh(row_ptr, col_idx, Q, K, V, scale, light_nodes, heavy_nodes, light_warps_per_block=4,
+                      heavy_warps_per_block=8):
+    """``(O [N,H,D], logsumexp [N,H])`` (``csrc/turbo_gnn.cpp:36-40``); score = <Q[src], K[dst]> * scale."""
+    _check_attention_inputs(Q, K, V)
+    _check_index_family(row_ptr, col_idx, light_nodes, heavy_nodes)
+    n_rows, heads, d = K.shape
+    lw, hw = _clamp_light(light_warps_per_block), _clamp_heavy(heavy_warps_per_block)
+    dp = _padded_head_dim(d)
+    q_in, k_in, v_in = _head_rows(Q, dp), _head_rows(K, dp), _head_rows(V, dp)
+    out = torch.empty((n_rows, heads, dp), dtype=Q.dtype, device=Q.device)
+    lse = torch.empty((n_rows, heads), dtype=torch.float32, device=Q.device)
+    if n_rows > 0:
+        sched = _sched(row_ptr, light_nodes, heavy_nodes)
+        ws, ws_bytes = _scratch(_abi.OP_GT_FWD, sched, q_in, row_ptr.dtype, heads * dp)
+        args = _abi.GtFwdArgs(
+            exec=_abi.exec_of(q_in),
+            csr=_abi.csr_of(row_ptr, col_idx, Q.shape[0]),
+            sched=sched.to_struct(lw, hw),
+            q=_abi.mat_of(q_in),
+            k=_abi.mat_of(k_in),
+            v=_abi.mat_of(v_in),
+            heads=heads,
+            head_dim=dp,
+            scale=float(scale),
+            out=_abi.mat_of(out),
+            lse=_abi.ptr(lse),
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
+        )
+        _abi.call("tgnn_gt_forward", args)
+    if dp != d:
+        out = out[..., :d].contiguous()
+    return out, lse
+
+
+def gt_backward_csr_mh(row_ptr, col_idx, row_ptr_T, col_idx_T, Q, K, V, O, dO, logsumexp, scale, light_nodes,
+                       heavy_nodes, light_warps_per_block=1, heavy_warps_per_block=8, is_directed=True,
+                       fwd_light_nodes=None, fwd_heavy_nodes=None):
+    """``(dQ, dK, dV)`` (``csrc/turbo_gnn.cpp:42-47``).
+
+    ``light_nodes``/``heavy_nodes`` bucket the transposed CSR (source-side pass: dQ, dV); the
+    destination-side pass (dK, forward CSR) uses ``fwd_light_nodes``/``fwd_heavy_nodes`` or, when
+    they are not given, a 0.99-quantile split computed here.
+    """
+    _check_attention_inputs(Q, K, V, O, dO)
+    _check_index_family(row_ptr, col_idx, row_ptr_T, col_idx_T, light_nodes, heavy_nodes)
+    n_rows, heads, d = K.shape
+    n_src = Q.shape[0]
+    lw, hw = _clamp_light(light_warps_per_block), _clamp_heavy(heavy_warps_per_block)
+    dp = _padded_head_dim(d)
+    q_in, k_in, v_in = _head_rows(Q, dp), _head_rows(K, dp), _head_rows(V, dp)
+    o_in = _head_rows(O.reshape(n_rows, heads, d), dp)
+    g_in = _head_rows(dO.reshape(n_rows, heads, d), dp)
+    lse = logsumexp.contiguous()
+    dq = torch.empty((n_src, heads, dp), dtype=Q.dtype, device=Q.device)
+    dv = torch.empty((n_src, heads, dp), dtype=Q.dtype, device=Q.device)
+    dk = torch.empty((n_rows, heads, dp), dtype=Q.dtype, device=Q.device)
+    if n_rows > 0:
+        if fwd_light_nodes is None or fwd_heavy_nodes is None:
+            fwd_light_nodes, fwd_heavy_nodes = _default_buckets(row_ptr)
+        delta = _head_dot(g_in, o_in, heads, dp)
+        ex = _abi.exec_of(q_in)
+        cols = heads * dp
+        f_sched = _sched(row_ptr, fwd_light_nodes, fwd_heavy_nodes)
+        ws, ws_bytes = _scratch(_abi.OP_GT_BWD_DST, f_sched, q_in, row_ptr.dtype, cols)
+        dst_args = _abi.GtBwdDstArgs(
+            exec=ex,
+            csr=_abi.csr_of(row_ptr, col_idx, n_src),
+            sched=f_sched.to_struct(lw, hw),
+            q=_abi.mat_of(q_in),
+            k=_abi.mat_of(k_in),
+            v=_abi.mat_of(v_in),
+            d_out=_abi.mat_of(g_in),
+            lse=_abi.ptr(lse),
+            delta=_abi.ptr(delta),
+            heads=heads,
+            head_dim=dp,
+            scale=float(scale),
+            dk=_abi.mat_of(dk),
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
+        )
+        _abi.call("tgnn_gt_backward_dst", dst_args)
+        b_sched = _sched(row_ptr_T, light_nodes, heavy_nodes)
+        ws2, ws2_bytes = _scratch(_abi.OP_GT_BWD_SRC, b_sched, q_in, row_ptr.dtype, cols)
+        src_args = _abi.GtBwdSrcArgs(
+            exec=ex,
+            csr_t=_abi.csr_of(row_ptr_T, col_idx_T, n_rows),
+            sched=b_sched.to_struct(lw, hw),
+            q=_abi.mat_of(q_in),
+            k=_abi.mat_of(k_in),
+            v=_abi.mat_of(v_in),
+            d_out=_abi.mat_of(g_in),
+            lse=_abi.ptr(lse),
+            delta=_abi.ptr(delta),
+            heads=heads,
+            head_dim=dp,
+            scale=float(scale),
+            dq=_abi.mat_of(dq),
+            dv=_abi.mat_of(dv),
+            workspace=_abi.ptr(ws2),
+            workspace_bytes=ws2_bytes,
+        )
+        _abi.call("tgnn_gt_backward_src", src_args)
+    else:
+        dq.zero_()
+        dv.zero_()
+    if dp != d:
+        dq, dk, dv = dq[..., :d].contiguous(), dk[..., :d].contiguous(), dv[..., :d].contiguous()
+    return dq, dk, dv

@@ -1,0 +1,403 @@
+"""ctypes binding of ``libturbo_gnn_b200.so`` (declared in ``include/tgnn_abi.h``).
+
+This module is the only place that touches the C ABI.  It mirrors the structs of
+the header field by field, loads the library lazily, and converts a non-zero
+status into ``RuntimeError`` carrying the library's message, which is what the
+autotuner relies on to skip launch parameters a kernel rejects (the reference
+signals the same condition with a C++ exception, ``csrc/common/traits.cuh:62-64``).
+
+There is no fallback: if the shared library has not been built, every op raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from pathlib import Path
+
+import torch
+
+LIB_NAME = "libturbo_gnn_b200.so"
+ABI_VERSION = 1
+
+OK = 0
+F32, F16, BF16 = 0, 1, 2
+I32, I64 = 0, 1
+REDUCE = {"min": 0, "max": 1, "sum": 2, "mean": 3}
+NORM = {"none": 0, "right": 1, "left": 2, "both": 3}
+OP_REDUCE_MINMAX, OP_WEIGHTED_SUM = 0, 1
+OP_GATV2_FWD, OP_GATV2_BWD_DST, OP_GATV2_BWD_SRC = 2, 3, 4
+OP_GT_FWD, OP_GT_BWD_DST, OP_GT_BWD_SRC = 5, 6, 7
+
+_DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+_ITYPES = {torch.int32: I32, torch.int64: I64, torch.uint32: I32, torch.uint64: I64}
+
+
+class Exec(C.Structure):
+    _fields_ = [("device", C.c_int32), ("_pad", C.c_int32), ("stream", C.c_void_p)]
+
+
+class Csr(C.Structure):
+    _fields_ = [
+        ("indptr", C.c_void_p),
+        ("indices", C.c_void_p),
+        ("num_rows", C.c_int64),
+        ("num_cols", C.c_int64),
+        ("num_edges", C.c_int64),
+        ("itype", C.c_int32),
+        ("_pad", C.c_int32),
+    ]
+
+
+class Schedule(C.Structure):
+    _fields_ = [
+        ("light_rows", C.c_void_p),
+        ("num_light", C.c_int64),
+        ("heavy_rows", C.c_void_p),
+        ("num_heavy", C.c_int64),
+        ("hub_rows", C.c_void_p),
+        ("num_hub", C.c_int64),
+        ("hub_part_ptr", C.c_void_p),
+        ("chunk_hub", C.c_void_p),
+        ("num_chunks", C.c_int64),
+        ("chunk_edges", C.c_int32),
+        ("light_warps", C.c_int32),
+        ("heavy_warps", C.c_int32),
+        ("_pad", C.c_int32),
+    ]
+
+
+class Mat(C.Structure):
+    _fields_ = [
+        ("data", C.c_void_p),
+        ("rows", C.c_int64),
+        ("cols", C.c_int64),
+        ("row_stride", C.c_int64),
+        ("dtype", C.c_int32),
+        ("_pad", C.c_int32),
+    ]
+
+
+class SegmentReduceArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr", Csr),
+        ("sched", Schedule),
+        ("x", Mat),
+        ("out", Mat),
+        ("arg_idx", C.c_void_p),
+        ("reduce", C.c_int32),
+        ("_pad", C.c_int32),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class SegmentReduceBwdArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("grad_out", Mat),
+        ("arg_idx", C.c_void_p),
+        ("grad_x", Mat),
+        ("itype", C.c_int32),
+        ("_pad", C.c_int32),
+    ]
+
+
+class DegreeNormArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr", Csr),
+        ("norm", C.c_int32),
+        ("_pad", C.c_int32),
+        ("row_scale", C.c_void_p),
+        ("col_scale", C.c_void_p),
+        ("col_count", C.c_void_p),
+    ]
+
+
+class SpmmArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr", Csr),
+        ("sched", Schedule),
+        ("x", Mat),
+        ("out", Mat),
+        ("row_scale", C.c_void_p),
+        ("col_scale", C.c_void_p),
+        ("edge_weight", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class HeadDotArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("a", Mat),
+        ("b", Mat),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("dot", C.c_void_p),
+    ]
+
+
+class Gatv2FwdArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr", Csr),
+        ("sched", Schedule),
+        ("l", Mat),
+        ("r", Mat),
+        ("attn", C.c_void_p),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("negative_slope", C.c_float),
+        ("_pad", C.c_int32),
+        ("out", Mat),
+        ("lse", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class Gatv2BwdDstArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr", Csr),
+        ("sched", Schedule),
+        ("grad_out", Mat),
+        ("l", Mat),
+        ("r", Mat),
+        ("attn", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("G", C.c_void_p),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("negative_slope", C.c_float),
+        ("_pad", C.c_int32),
+        ("grad_l", Mat),
+        ("grad_attn_f32", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class Gatv2BwdSrcArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr_t", Csr),
+        ("sched", Schedule),
+        ("grad_out", Mat),
+        ("l", Mat),
+        ("r", Mat),
+        ("attn", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("G", C.c_void_p),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("negative_slope", C.c_float),
+        ("_pad", C.c_int32),
+        ("grad_r", Mat),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class GtFwdArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr", Csr),
+        ("sched", Schedule),
+        ("q", Mat),
+        ("k", Mat),
+        ("v", Mat),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("scale", C.c_float),
+        ("_pad", C.c_int32),
+        ("out", Mat),
+        ("lse", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class GtBwdDstArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr", Csr),
+        ("sched", Schedule),
+        ("q", Mat),
+        ("k", Mat),
+        ("v", Mat),
+        ("d_out", Mat),
+        ("lse", C.c_void_p),
+        ("delta", C.c_void_p),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("scale", C.c_float),
+        ("_pad", C.c_int32),
+        ("dk", Mat),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class GtBwdSrcArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr_t", Csr),
+        ("sched", Schedule),
+        ("q", Mat),
+        ("k", Mat),
+        ("v", Mat),
+        ("d_out", Mat),
+        ("lse", C.c_void_p),
+        ("delta", C.c_void_p),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("scale", C.c_float),
+        ("_pad", C.c_int32),
+        ("dq", Mat),
+        ("dv", Mat),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+# symbol -> argument struct (None = takes no struct); every symbol the header declares.
+ENTRY_POINTS = {
+    "tgnn_abi_version": None,
+    "tgnn_last_error": None,
+    "tgnn_workspace_bytes": None,
+    "tgnn_segment_reduce_forward": SegmentReduceArgs,
+    "tgnn_segment_reduce_backward": SegmentReduceBwdArgs,
+    "tgnn_degree_norm": DegreeNormArgs,
+    "tgnn_spmm": SpmmArgs,
+    "tgnn_head_dot": HeadDotArgs,
+    "tgnn_gatv2_forward": Gatv2FwdArgs,
+    "tgnn_gatv2_backward_dst": Gatv2BwdDstArgs,
+    "tgnn_gatv2_backward_src": Gatv2BwdSrcArgs,
+    "tgnn_gt_forward": GtFwdArgs,
+    "tgnn_gt_backward_dst": GtBwdDstArgs,
+    "tgnn_gt_backward_src": GtBwdSrcArgs,
+}
+
+_lib = None
+_lib_lock = threading.Lock()
+
+
+def library_path() -> Path:
+    return Path(__file__).resolve().parent / LIB_NAME
+
+
+def load_library() -> C.CDLL:
+    """Load the shared library once; raise if it is missing or of another ABI version."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lib_lock:
+        if _lib is not None:
+            return _lib
+        path = library_path()
+        if not path.exists():
+            raise RuntimeError(
+                f"{path} is missing: build it with `python -m turbo_gnn_b200.build`. "
+                "turbo_gnn_b200 has no CPU or PyTorch fallback for its CUDA kernels."
+            )
+        lib = C.CDLL(str(path))
+        lib.tgnn_abi_version.restype = C.c_int32
+        lib.tgnn_abi_version.argtypes = []
+        lib.tgnn_last_error.restype = None
+        lib.tgnn_last_error.argtypes = [C.c_char_p, C.c_size_t]
+        lib.tgnn_workspace_bytes.restype = C.c_size_t
+        lib.tgnn_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]
+        for name, struct in ENTRY_POINTS.items():
+            fn = getattr(lib, name)  # AttributeError here = header and binary disagree
+            if struct is not None:
+                fn.restype = C.c_int32
+                fn.argtypes = [C.POINTER(struct)]
+        got = lib.tgnn_abi_version()
+        if got != ABI_VERSION:
+            raise RuntimeError(f"{path} has ABI version {got}, this package expects {ABI_VERSION}; rebuild it")
+        _lib = lib
+    return _lib
+
+
+def last_error() -> str:
+    buf = C.create_string_buffer(512)
+    load_library().tgnn_last_error(buf, len(buf))
+    return buf.value.decode(errors="replace")
+
+
+def call(name: str, args: C.Structure) -> None:
+    """Invoke an entry point; a non-zero status becomes RuntimeError."""
+    status = getattr(load_library(), name)(C.byref(args))
+    if status != OK:
+        raise RuntimeError(f"{name} failed with status {status}: {last_error()}")
+
+
+def workspace_bytes(op: int, dtype: torch.dtype, itype: torch.dtype, num_chunks: int, cols: int) -> int:
+    return int(load_library().tgnn_workspace_bytes(op, dtype_code(dtype), itype_code(itype), num_chunks, cols))
+
+
+# ---- torch tensor -> struct helpers --------------------------------------------------
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPES[dt]
+    except KeyError:
+        raise RuntimeError(f"features must be float32/float16/bfloat16, got {dt}") from None
+
+
+def itype_code(dt: torch.dtype) -> int:
+    try:
+        return _ITYPES[dt]
+    except KeyError:
+        raise RuntimeError(f"index tensors must be int32, int64, uint32 or uint64, got {dt}") from None
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    if t is None or t.numel() == 0:
+        return None
+    return t.data_ptr()
+
+
+def exec_of(t: torch.Tensor) -> Exec:
+    if not t.is_cuda:
+        raise RuntimeError("turbo_gnn_b200 kernels need CUDA tensors; there is no CPU path")
+    dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    return Exec(device=dev, stream=torch.cuda.current_stream(dev).cuda_stream)
+
+
+def mat_of(t: torch.Tensor) -> Mat:
+    """View a 2-D (or [N,H,D] with head stride D) tensor as a row-major matrix."""
+    if t.dim() == 3:
+        n, h, d = t.shape
+        if t.stride(2) != 1 or (h > 1 and t.stride(1) != d):
+            raise RuntimeError("expected [N, H, D] with contiguous heads")
+        cols, stride = h * d, (t.stride(0) if n > 1 else h * d)
+    elif t.dim() == 2:
+        if t.shape[1] > 1 and t.stride(1) != 1:
+            raise RuntimeError("expected a row-major matrix")
+        cols, stride = t.shape[1], (t.stride(0) if t.shape[0] > 1 else t.shape[1])
+    else:
+        raise RuntimeError(f"expected a 2-D or 3-D tensor, got {t.dim()}-D")
+    return Mat(data=ptr(t), rows=t.shape[0], cols=cols, row_stride=max(stride, cols), dtype=dtype_code(t.dtype))
+
+
+def csr_of(indptr: torch.Tensor, indices: torch.Tensor, num_cols: int) -> Csr:
+    if indptr.dtype != indices.dtype:
+        raise RuntimeError("indptr and indices must share a dtype")
+    if not (indptr.is_contiguous() and indices.is_contiguous()):
+        raise RuntimeError("CSR arrays must be contiguous")
+    return Csr(
+        indptr=indptr.data_ptr(),
+        indices=ptr(indices),
+        num_rows=indptr.numel() - 1,
+        num_cols=num_cols,
+        num_edges=indices.numel(),
+        itype=itype_code(indptr.dtype),
+    )

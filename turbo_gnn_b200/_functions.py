@@ -1,0 +1,303 @@
+"""Autograd bridges between the public ops and the kernel library.
+
+Mirrors the reference's ``turbo_gnn/_functions.py``: the same four
+``torch.autograd.Function`` classes with the same positional ``apply`` orders
+(``_functions.py:32-106`` reduction, ``:109-232`` GATv2, ``:235-335`` graph
+transformer, ``:338-374`` SpMM), because the reference's tests call ``apply``
+positionally.  AMP behaviour is kept: reduction casts ``X`` and GATv2 casts the
+attention vector to the autocast dtype.
+"""
+
+from __future__ import annotations
+
+import warnings
+from math import ceil
+
+import torch
+
+from . import _C
+
+WARP_SIZE = 32
+_VALID_BLOCK_WARPS = (1, 2, 4, 8, 16, 32, 64)
+
+
+def _next_power_of_two(x: int) -> int:
+    return 1 if x <= 1 else 1 << (int(x) - 1).bit_length()
+
+
+def _fit_warps_to_features(requested: int, feat: int, itemsize: int) -> int:
+    """Clamp a requested block width to what `feat` features can occupy (one 4-byte slot per thread).
+
+    Same rule and warning as the reference (``_functions.py:63-79``): a block wider than the
+    feature row only adds idle threads.
+    """
+    threads_needed = ceil(feat / max(4 // itemsize, 1))
+    if threads_needed >= WARP_SIZE * requested:
+        return requested
+    needed = ceil(threads_needed / WARP_SIZE)
+    warnings.warn(
+        f"Number of threads involved for ReductionAggr is {WARP_SIZE * requested} "
+        f"({requested} warps per thread block requested). "
+        f"However, number of threads needed is {threads_needed} ({needed} warps). Setting this value instead."
+    )
+    return needed if needed in _VALID_BLOCK_WARPS else _next_power_of_two(needed)
+
+
+class ReductionAggrFunction(torch.autograd.Function):
+    """Segment min / max (also sum / mean) over the forward CSR; backward routes grads to the winners."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(
+        ctx,
+        edge_ptr,
+        edge_idx,
+        X,
+        light,
+        heavy,
+        max_degree,
+        warps_per_block,
+        edges_per_block_heavy_nodes,
+        use_2d_kernel=False,
+        features_per_block=32,
+        tiles_y=8,
+        reduce="min",
+    ):
+        if torch.is_autocast_enabled():
+            X = X.to(torch.get_autocast_gpu_dtype())
+        warps_per_block = _fit_warps_to_features(warps_per_block, X.shape[-1], X.dtype.itemsize)
+        needs_grad = ctx.needs_input_grad[2]
+        out, arg_idx = _C.reduction_aggr_forward_partitioned(
+            edge_ptr,
+            edge_idx,
+            X,
+            light,
+            heavy,
+            max_degree,
+            warps_per_block,
+            edges_per_block_heavy_nodes,
+            use_2d_kernel,
+            features_per_block,
+            tiles_y,
+            reduce,
+            want_arg=needs_grad,
+        )
+        ctx.reduce = reduce
+        ctx.num_src_nodes = X.size(0)
+        ctx.warps_per_block = warps_per_block
+        if reduce in ("min", "max"):
+            ctx.save_for_backward(*([arg_idx] if arg_idx is not None else []))
+        else:
+            ctx.save_for_backward(edge_ptr, edge_idx)
+        return out
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_out):
+        if ctx.reduce in ("min", "max"):
+            (arg_idx,) = ctx.saved_tensors
+            grad_x = _C.reduction_aggr_backward(grad_out.contiguous(), arg_idx, ctx.num_src_nodes, ctx.warps_per_block)
+        else:
+            edge_ptr, edge_idx = ctx.saved_tensors
+            grad_x = _C.csr_SPMM_normalized(
+                edge_ptr, edge_idx, grad_out.contiguous(), None, "right" if ctx.reduce == "mean" else "none",
+                do_transpose_a=True,
+            )
+        return (None, None, grad_x) + (None,) * 9
+
+
+class gatv2_function(torch.autograd.Function):
+    """Fused GATv2 aggregation: edge score -> LeakyReLU -> online segment softmax -> weighted gather."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(
+        ctx,
+        indptr_forward,
+        indices_forward,
+        indptr_backward,
+        indices_backward,
+        x_left,
+        x_right,
+        attention_weights,
+        negative_slope,
+        grad_A_reduce_row_chunk_size,
+        fwd_light_nodes,
+        fwd_heavy_nodes,
+        bwd_light_nodes,
+        bwd_heavy_nodes,
+        forward_light_warps,
+        forward_heavy_warps,
+        backward_light_warps,
+        backward_heavy_warps,
+        is_directed,
+    ):
+        if torch.is_autocast_enabled():
+            attention_weights = attention_weights.to(torch.get_autocast_gpu_dtype())
+        output, logsumexp = _C.gatv2_forward(
+            x_left,
+            x_right,
+            indptr_forward,
+            indices_forward,
+            attention_weights,
+            negative_slope,
+            fwd_light_nodes,
+            fwd_heavy_nodes,
+            forward_light_warps,
+            forward_heavy_warps,
+        )
+        ctx.negative_slope = negative_slope
+        ctx.hub_cfg = _C.current_hub_config()
+        ctx.grad_A_reduce_row_chunk_size = grad_A_reduce_row_chunk_size
+        ctx.launch = (backward_light_warps, backward_heavy_warps)
+        ctx.is_directed = is_directed
+        ctx.head_shape = (x_left.shape[1], x_left.shape[2])
+        # The output is kept as well: <grad_out, out> per head replaces a neighbour sweep in backward.
+        ctx.save_for_backward(
+            x_left,
+            x_right,
+            indptr_forward,
+            indices_forward,
+            indptr_backward,
+            indices_backward,
+            attention_weights,
+            logsumexp,
+            fwd_light_nodes,
+            fwd_heavy_nodes,
+            bwd_light_nodes,
+            bwd_heavy_nodes,
+            output,
+        )
+        return output
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_output):
+        (x_left, x_right, ptr_f, idx_f, ptr_b, idx_b, attn, lse, f_light, f_heavy, b_light, b_heavy, out) = (
+            ctx.saved_tensors
+        )
+        heads, head_dim = ctx.head_shape
+        grad_output = grad_output.reshape(-1, heads, head_dim)
+        with _C.hub_tier(**ctx.hub_cfg):
+            grad_left, grad_right, grad_attn = _C.gatv2_backward(
+                grad_output, x_left, x_right, ptr_f, idx_f, ptr_b, idx_b, attn, lse, ctx.negative_slope,
+                ctx.grad_A_reduce_row_chunk_size, f_light, f_heavy, b_light, b_heavy, ctx.launch[0], ctx.launch[1],
+                ctx.is_directed, out=out,
+            )
+        return (None, None, None, None, grad_left, grad_right, grad_attn) + (None,) * 11
+
+
+class _FusedGraphAttention(torch.autograd.Function):
+    """Fused sparse multi-head attention: (Q[src] . K[dst]) * scale -> segment softmax -> sum alpha V[src]."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(
+        ctx,
+        edge_ptr,
+        edge_idx,
+        edge_ptr_T,
+        edge_idx_T,
+        Q,
+        K,
+        V,
+        scale,
+        fwd_light_nodes,
+        fwd_heavy_nodes,
+        bwd_light_nodes,
+        bwd_heavy_nodes,
+        forward_light_warps,
+        forward_heavy_warps,
+        backward_light_warps,
+        backward_heavy_warps,
+        is_directed,
+    ):
+        scale = scale or 1 / (Q.shape[-1] ** 0.5)
+        out, logsumexp = _C.gt_forward_csr_mh(
+            edge_ptr, edge_idx, Q, K, V, scale, fwd_light_nodes, fwd_heavy_nodes, forward_light_warps,
+            forward_heavy_warps,
+        )
+        ctx.scale = scale
+        ctx.hub_cfg = _C.current_hub_config()
+        ctx.is_directed = is_directed
+        ctx.head_shape = (Q.shape[1], Q.shape[2])
+        ctx.launch = (backward_light_warps, backward_heavy_warps)
+        ctx.save_for_backward(
+            edge_ptr, edge_idx, edge_ptr_T, edge_idx_T, Q, K, V, out, logsumexp, fwd_light_nodes, fwd_heavy_nodes,
+            bwd_light_nodes, bwd_heavy_nodes,
+        )
+        return out
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_output):
+        (ptr, idx, ptr_t, idx_t, Q, K, V, out, lse, f_light, f_heavy, b_light, b_heavy) = ctx.saved_tensors
+        heads, head_dim = ctx.head_shape
+        grad_output = grad_output.reshape(-1, heads, head_dim)
+        with _C.hub_tier(**ctx.hub_cfg):
+            dQ, dK, dV = _C.gt_backward_csr_mh(
+                ptr, idx, ptr_t, idx_t, Q, K, V, out, grad_output, lse, ctx.scale, b_light, b_heavy, ctx.launch[0],
+                ctx.launch[1], ctx.is_directed, fwd_light_nodes=f_light, fwd_heavy_nodes=f_heavy,
+            )
+        return (None,) * 4 + (dQ, dK, dV) + (None,) * 10
+
+
+class _CudaSpMMConvFn(torch.autograd.Function):
+    """Normalised SpMM over a forward CSR; backward multiplies by the transposed, equally normalised matrix."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, x, forward_indptr, forward_indices, norm_type, cu_sparse_algorithm_id, block_dim):
+        ctx.save_for_backward(forward_indptr, forward_indices)
+        ctx.cfg = (norm_type, cu_sparse_algorithm_id, block_dim)
+        return csr_SPMM_normalized(
+            indptr=forward_indptr,
+            indices=forward_indices,
+            features=x,
+            edge_weights=None,
+            norm=norm_type,
+            algorithm=cu_sparse_algorithm_id,
+            do_transpose_a=False,
+            block_dim=block_dim,
+        )
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, *grad_outputs):
+        forward_indptr, forward_indices = ctx.saved_tensors
+        norm_type, alg, block_dim = ctx.cfg
+        grad_x = csr_SPMM_normalized(
+            indptr=forward_indptr,
+            indices=forward_indices,
+            features=grad_outputs[0],
+            edge_weights=None,
+            norm=norm_type,
+            algorithm=alg,
+            do_transpose_a=True,
+            block_dim=block_dim,
+        )
+        return grad_x, None, None, None, None, None
+
+
+def csr_SPMM_normalized(
+    indptr,
+    indices,
+    features,
+    edge_weights=None,
+    norm="none",
+    algorithm=-1,
+    use_cache=True,
+    do_transpose_a=False,
+    block_dim=256,
+):
+    """``norm(A) @ features`` with norm in none (sum) / right (mean) / left / both (GCN).
+
+    Keyword-friendly wrapper of the kernel entry (reference: ``_functions.py:377-417``).
+    ``edge_weights`` ([E], optional) multiply the normalisation weights.
+    """
+    w = None
+    if edge_weights is not None:
+        w = edge_weights.to(device=features.device, dtype=torch.float32)
+    return _C.csr_SPMM_normalized(
+        indptr, indices, features.contiguous(), w, norm, algorithm, use_cache, do_transpose_a, block_dim
+    )

@@ -1,0 +1,134 @@
+// Library-level entry points and the argument checks shared by every op.
+#include <cstring>
+#include <mutex>
+
+#include "dispatch.cuh"
+
+namespace tgnn {
+
+char *error_buffer() {
+    static thread_local char buf[kErrorBufferLen] = {0};
+    return buf;
+}
+
+int sm_count(int device) {
+    static std::mutex mu;
+    static int cached[64] = {0};
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 0 || device >= 64) return 148;
+    if (cached[device] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+        cached[device] = n;
+    }
+    return cached[device];
+}
+
+int32_t check_exec(const tgnn_exec &e) {
+    TGNN_REQUIRE(e.device >= 0, TGNN_ERR_INVALID_ARGUMENT, "device ordinal %d is negative", e.device);
+    TGNN_CUDA(cudaSetDevice(e.device));
+    return TGNN_OK;
+}
+
+int32_t check_csr(const tgnn_csr &c) {
+    TGNN_REQUIRE(c.itype == TGNN_I32 || c.itype == TGNN_I64, TGNN_ERR_INVALID_ARGUMENT, "unknown index type %d",
+                 c.itype);
+    TGNN_REQUIRE(c.num_rows >= 0 && c.num_cols >= 0 && c.num_edges >= 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "negative CSR extent");
+    TGNN_REQUIRE(c.indptr != nullptr, TGNN_ERR_INVALID_ARGUMENT, "indptr is null");
+    TGNN_REQUIRE(c.indices != nullptr || c.num_edges == 0, TGNN_ERR_INVALID_ARGUMENT, "indices is null");
+    if (c.itype == TGNN_I32)
+        TGNN_REQUIRE(c.num_edges < (1ll << 31) && c.num_cols < (1ll << 31) && c.num_rows < (1ll << 31),
+                     TGNN_ERR_INVALID_ARGUMENT, "graph too large for 32-bit indices");
+    return TGNN_OK;
+}
+
+int32_t check_schedule(const tgnn_schedule &s, const tgnn_csr &c) {
+    TGNN_REQUIRE(s.num_light >= 0 && s.num_heavy >= 0 && s.num_hub >= 0 && s.num_chunks >= 0,
+                 TGNN_ERR_INVALID_ARGUMENT, "negative schedule extent");
+    TGNN_REQUIRE(s.num_light == 0 || s.light_rows != nullptr, TGNN_ERR_INVALID_ARGUMENT, "light_rows is null");
+    TGNN_REQUIRE(s.num_heavy == 0 || s.heavy_rows != nullptr, TGNN_ERR_INVALID_ARGUMENT, "heavy_rows is null");
+    TGNN_REQUIRE(s.num_light <= c.num_rows && s.num_heavy <= c.num_rows && s.num_hub <= c.num_rows,
+                 TGNN_ERR_INVALID_ARGUMENT, "a row list is longer than the CSR has rows");
+    if (s.num_light > 0)
+        TGNN_REQUIRE(s.light_warps == 1 || s.light_warps == 2 || s.light_warps == 4 || s.light_warps == 8,
+                     TGNN_ERR_LAUNCH_PARAM, "Wrong int value: light warps %d not in {1,2,4,8}", s.light_warps);
+    if (s.num_heavy > 0 || s.num_hub > 0)
+        TGNN_REQUIRE(s.heavy_warps >= 1 && s.heavy_warps <= 16, TGNN_ERR_LAUNCH_PARAM,
+                     "Wrong int value: heavy warps %d not in 1..16", s.heavy_warps);
+    if (s.num_hub > 0) {
+        TGNN_REQUIRE(s.hub_rows != nullptr && s.hub_part_ptr != nullptr && s.chunk_hub != nullptr,
+                     TGNN_ERR_INVALID_ARGUMENT, "hub tier arrays are null");
+        TGNN_REQUIRE(s.num_chunks >= s.num_hub && s.num_chunks < (1ll << 31), TGNN_ERR_INVALID_ARGUMENT,
+                     "hub chunk count %lld out of range", static_cast<long long>(s.num_chunks));
+        TGNN_REQUIRE(s.chunk_edges >= 32 && s.chunk_edges <= 65536 && s.chunk_edges % 32 == 0,
+                     TGNN_ERR_LAUNCH_PARAM, "Wrong int value: chunk_edges %d", s.chunk_edges);
+    }
+    return TGNN_OK;
+}
+
+int32_t check_mat(const tgnn_mat &m, const char *name, int64_t rows, int64_t cols, int32_t dtype) {
+    TGNN_REQUIRE(m.dtype == TGNN_F32 || m.dtype == TGNN_F16 || m.dtype == TGNN_BF16, TGNN_ERR_INVALID_ARGUMENT,
+                 "%s: unknown element type %d", name, m.dtype);
+    TGNN_REQUIRE(dtype < 0 || m.dtype == dtype, TGNN_ERR_INVALID_ARGUMENT, "%s: element type differs from the others",
+                 name);
+    TGNN_REQUIRE(m.rows == rows, TGNN_ERR_INVALID_ARGUMENT, "%s: %lld rows, expected %lld", name,
+                 static_cast<long long>(m.rows), static_cast<long long>(rows));
+    TGNN_REQUIRE(m.cols == cols, TGNN_ERR_INVALID_ARGUMENT, "%s: %lld columns, expected %lld", name,
+                 static_cast<long long>(m.cols), static_cast<long long>(cols));
+    TGNN_REQUIRE(m.row_stride >= m.cols, TGNN_ERR_INVALID_ARGUMENT, "%s: row stride below the column count", name);
+    TGNN_REQUIRE(m.data != nullptr || m.rows == 0, TGNN_ERR_INVALID_ARGUMENT, "%s: null data", name);
+    const int64_t chunk = 16 / static_cast<int64_t>(dtype_size(m.dtype));
+    TGNN_REQUIRE(m.cols > 0 && m.cols % chunk == 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "%s: column count %lld is not a positive multiple of %lld", name, static_cast<long long>(m.cols),
+                 static_cast<long long>(chunk));
+    TGNN_REQUIRE(aligned16(m.data) && m.row_stride % chunk == 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "%s: base address or row pitch not 16-byte aligned", name);
+    return TGNN_OK;
+}
+
+Geometry make_geometry(int64_t cols, int chunk_elems, int min_group_lanes) {
+    const int64_t chunks = (cols + chunk_elems - 1) / chunk_elems;
+    Geometry g;
+    g.slices = 1;
+    if (chunks <= 32) {
+        g.vpl = 1;
+        g.G = ilog2_ceil_pow2(static_cast<int>(chunks));
+        if (g.G < min_group_lanes) g.G = min_group_lanes;
+        if (g.G > 32) g.G = 32;
+    } else {
+        g.G = 32;
+        g.vpl = chunks <= 64 ? 2 : (chunks <= 128 ? 4 : 8);
+        g.slices = static_cast<int>((chunks + 255) / 256);
+    }
+    return g;
+}
+
+}  // namespace tgnn
+
+extern "C" {
+
+int32_t tgnn_abi_version(void) { return TGNN_ABI_VERSION; }
+
+void tgnn_last_error(char *buf, size_t buf_len) {
+    if (buf == nullptr || buf_len == 0) return;
+    strncpy(buf, tgnn::error_buffer(), buf_len - 1);
+    buf[buf_len - 1] = '\0';
+}
+
+size_t tgnn_workspace_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_chunks, int64_t feat_cols) {
+    if (num_chunks <= 0 || feat_cols <= 0) return 0;
+    switch (op) {
+        case TGNN_OP_REDUCE_MINMAX:
+        case TGNN_OP_WEIGHTED_SUM: return tgnn::reduce_scratch_bytes(op, dtype, itype, num_chunks, feat_cols);
+        case TGNN_OP_GATV2_FWD:
+        case TGNN_OP_GATV2_BWD_DST:
+        case TGNN_OP_GATV2_BWD_SRC: return tgnn::gatv2_scratch_bytes(op, dtype, itype, num_chunks, feat_cols);
+        case TGNN_OP_GT_FWD:
+        case TGNN_OP_GT_BWD_DST:
+        case TGNN_OP_GT_BWD_SRC: return tgnn::gt_scratch_bytes(op, dtype, itype, num_chunks, feat_cols);
+        default: return 0;
+    }
+}
+
+}  // extern "C"

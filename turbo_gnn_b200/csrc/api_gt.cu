@@ -1,0 +1,159 @@
+// C-ABI entry points of the fused graph-transformer attention.
+#include "dispatch.cuh"
+#include "ops_gt.cuh"
+
+namespace tgnn {
+
+namespace {
+
+int32_t check_gt_heads(int heads, int head_dim, int64_t cols) {
+    TGNN_REQUIRE(heads > 0 && head_dim > 0 && static_cast<int64_t>(heads) * head_dim == cols,
+                 TGNN_ERR_INVALID_ARGUMENT, "heads (%d) x head_dim (%d) does not match the row width %lld", heads,
+                 head_dim, static_cast<long long>(cols));
+    TGNN_REQUIRE(head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256,
+                 TGNN_ERR_UNSUPPORTED, "head_dim %d not in {16, 32, 64, 128, 256}", head_dim);
+    return TGNN_OK;
+}
+
+Geometry gt_geometry(int64_t cols, int head_dim, int32_t dtype) {
+    const int per = dtype == TGNN_F32 ? 4 : 8;
+    int lanes_per_head = head_dim / per;
+    if (lanes_per_head > 32) lanes_per_head = 32;
+    return make_geometry(cols, per, lanes_per_head);
+}
+
+template <typename T>
+GtParams<T> base_params(const tgnn_mat &q, const tgnn_mat &k, const tgnn_mat &v, int heads, int head_dim,
+                        float scale) {
+    GtParams<T> p{};
+    p.q = static_cast<const T *>(q.data);
+    p.ldq = q.row_stride;
+    p.k = static_cast<const T *>(k.data);
+    p.ldk = k.row_stride;
+    p.v = static_cast<const T *>(v.data);
+    p.ldv = v.row_stride;
+    p.cols = static_cast<int>(q.cols);
+    p.heads = heads;
+    p.head_dim = head_dim;
+    p.scale = scale;
+    return p;
+}
+
+template <template <typename, typename, int> class OpT>
+size_t words_of(int32_t dtype, int32_t itype, int vpl) {
+    size_t words = 0;
+    dispatch_tiv(dtype, itype, vpl, [&](auto tt, auto it, auto vt) -> int32_t {
+        using T = typename decltype(tt)::type;
+        using I = typename decltype(it)::type;
+        words = OpT<T, I, decltype(vt)::value>::kWords;
+        return TGNN_OK;
+    });
+    return words;
+}
+
+}  // namespace
+
+size_t gt_scratch_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_chunks, int64_t cols) {
+    const int per = dtype == TGNN_F32 ? 4 : 8;
+    const Geometry geo = make_geometry(cols, per, 1);
+    size_t words = 0;
+    if (op == TGNN_OP_GT_FWD) words = words_of<GtFwdOp>(dtype, itype, geo.vpl);
+    if (op == TGNN_OP_GT_BWD_DST) words = words_of<GtBwdDstOp>(dtype, itype, geo.vpl);
+    if (op == TGNN_OP_GT_BWD_SRC) words = words_of<GtBwdSrcOp>(dtype, itype, geo.vpl);
+    return static_cast<size_t>(num_chunks) * geo.slices * words * 32 * sizeof(uint32_t);
+}
+
+}  // namespace tgnn
+
+using namespace tgnn;
+
+extern "C" int32_t tgnn_gt_forward(const tgnn_gt_fwd_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));
+    TGNN_TRY(check_csr(a->csr));
+    TGNN_TRY(check_schedule(a->sched, a->csr));
+    const int64_t cols = a->q.cols;
+    TGNN_TRY(check_mat(a->q, "Q", a->csr.num_cols, cols, -1));
+    TGNN_TRY(check_mat(a->k, "K", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_mat(a->v, "V", a->csr.num_cols, cols, a->q.dtype));
+    TGNN_TRY(check_mat(a->out, "out", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_gt_heads(a->heads, a->head_dim, cols));
+    TGNN_REQUIRE(a->lse != nullptr || a->csr.num_rows == 0, TGNN_ERR_INVALID_ARGUMENT, "lse is null");
+    if (a->csr.num_rows == 0) return TGNN_OK;
+    const Geometry geo = gt_geometry(cols, a->head_dim, a->q.dtype);
+    return dispatch_tiv(a->q.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
+        using T = typename decltype(tt)::type;
+        using I = typename decltype(it)::type;
+        auto p = base_params<T>(a->q, a->k, a->v, a->heads, a->head_dim, a->scale);
+        p.out0 = static_cast<T *>(a->out.data);
+        p.ldo0 = a->out.row_stride;
+        p.lse_out = a->lse;
+        return run_tiers<GtFwdOp<T, I, decltype(vt)::value>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
+                                                             a->workspace_bytes, false);
+    });
+}
+
+extern "C" int32_t tgnn_gt_backward_dst(const tgnn_gt_bwd_dst_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));
+    TGNN_TRY(check_csr(a->csr));
+    TGNN_TRY(check_schedule(a->sched, a->csr));
+    const int64_t cols = a->q.cols;
+    TGNN_TRY(check_mat(a->q, "Q", a->csr.num_cols, cols, -1));
+    TGNN_TRY(check_mat(a->k, "K", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_mat(a->v, "V", a->csr.num_cols, cols, a->q.dtype));
+    TGNN_TRY(check_mat(a->d_out, "dO", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_mat(a->dk, "dK", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_gt_heads(a->heads, a->head_dim, cols));
+    TGNN_REQUIRE((a->lse != nullptr && a->delta != nullptr) || a->csr.num_rows == 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "lse or delta is null");
+    if (a->csr.num_rows == 0) return TGNN_OK;
+    const Geometry geo = gt_geometry(cols, a->head_dim, a->q.dtype);
+    return dispatch_tiv(a->q.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
+        using T = typename decltype(tt)::type;
+        using I = typename decltype(it)::type;
+        auto p = base_params<T>(a->q, a->k, a->v, a->heads, a->head_dim, a->scale);
+        p.d_out = static_cast<const T *>(a->d_out.data);
+        p.ldd = a->d_out.row_stride;
+        p.lse = a->lse;
+        p.delta = a->delta;
+        p.out0 = static_cast<T *>(a->dk.data);
+        p.ldo0 = a->dk.row_stride;
+        return run_tiers<GtBwdDstOp<T, I, decltype(vt)::value>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
+                                                                a->workspace_bytes, false);
+    });
+}
+
+extern "C" int32_t tgnn_gt_backward_src(const tgnn_gt_bwd_src_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));
+    TGNN_TRY(check_csr(a->csr_t));
+    TGNN_TRY(check_schedule(a->sched, a->csr_t));
+    const int64_t cols = a->q.cols;
+    TGNN_TRY(check_mat(a->q, "Q", a->csr_t.num_rows, cols, -1));
+    TGNN_TRY(check_mat(a->v, "V", a->csr_t.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_mat(a->k, "K", a->csr_t.num_cols, cols, a->q.dtype));
+    TGNN_TRY(check_mat(a->d_out, "dO", a->csr_t.num_cols, cols, a->q.dtype));
+    TGNN_TRY(check_mat(a->dq, "dQ", a->csr_t.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_mat(a->dv, "dV", a->csr_t.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_gt_heads(a->heads, a->head_dim, cols));
+    TGNN_REQUIRE((a->lse != nullptr && a->delta != nullptr) || a->csr_t.num_cols == 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "lse or delta is null");
+    if (a->csr_t.num_rows == 0) return TGNN_OK;
+    const Geometry geo = gt_geometry(cols, a->head_dim, a->q.dtype);
+    return dispatch_tiv(a->q.dtype, a->csr_t.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
+        using T = typename decltype(tt)::type;
+        using I = typename decltype(it)::type;
+        auto p = base_params<T>(a->q, a->k, a->v, a->heads, a->head_dim, a->scale);
+        p.d_out = static_cast<const T *>(a->d_out.data);
+        p.ldd = a->d_out.row_stride;
+        p.lse = a->lse;
+        p.delta = a->delta;
+        p.out0 = static_cast<T *>(a->dq.data);
+        p.ldo0 = a->dq.row_stride;
+        p.out1 = static_cast<T *>(a->dv.data);
+        p.ldo1 = a->dv.row_stride;
+        return run_tiers<GtBwdSrcOp<T, I, decltype(vt)::value>>(p, a->csr_t, a->sched, a->exec, geo, a->workspace,
+                                                                a->workspace_bytes, false);
+    });
+}

@@ -1,0 +1,228 @@
+// C-ABI entry points of the segment reductions and the weighted sum (g-SpMM).
+#include "dispatch.cuh"
+#include "ops_reduce.cuh"
+
+namespace tgnn {
+
+namespace {
+
+template <typename T, typename I>
+ReduceParams<T, I> make_params(const tgnn_mat &x, const tgnn_mat &out, void *arg) {
+    ReduceParams<T, I> p;
+    p.x = static_cast<const T *>(x.data);
+    p.ldx = x.row_stride;
+    p.out = static_cast<T *>(out.data);
+    p.ldo = out.row_stride;
+    p.arg = static_cast<I *>(arg);
+    p.cols = static_cast<int>(x.cols);
+    p.row_scale = nullptr;
+    p.col_scale = nullptr;
+    p.edge_weight = nullptr;
+    p.mean_by_degree = 0;
+    return p;
+}
+
+int32_t check_reduce_io(const tgnn_exec &ex, const tgnn_csr &csr, const tgnn_schedule &s, const tgnn_mat &x,
+                        const tgnn_mat &out) {
+    TGNN_TRY(check_exec(ex));
+    TGNN_TRY(check_csr(csr));
+    TGNN_TRY(check_schedule(s, csr));
+    TGNN_REQUIRE(x.cols < (1ll << 30), TGNN_ERR_INVALID_ARGUMENT, "feature count too large");
+    TGNN_TRY(check_mat(x, "x", csr.num_cols, x.cols, -1));
+    TGNN_TRY(check_mat(out, "out", csr.num_rows, x.cols, x.dtype));
+    return TGNN_OK;
+}
+
+// One thread per 16-byte chunk of grad_out; each element goes to its winner row.
+template <typename T, typename I>
+__global__ void __launch_bounds__(256) scatter_to_winner_kernel(const T *__restrict__ grad_out, int64_t ldg,
+                                                                 const I *__restrict__ arg, T *__restrict__ grad_x,
+                                                                 int64_t ldx, int64_t rows, int cols) {
+    constexpr int kPer = Elem<T>::kPerChunk;
+    const int chunks = cols / kPer;
+    const int64_t total = rows * chunks;
+    for (int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+         t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t v = t / chunks;
+        const int off = static_cast<int>(t - v * chunks) * kPer;
+        const uint4 raw = ld_stream16(grad_out + v * ldg + off);
+        const T *g = reinterpret_cast<const T *>(&raw);
+        const I *a = arg + v * cols + off;
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) {
+            const I src = a[e];
+            if (src >= 0) atomicAdd(grad_x + static_cast<int64_t>(src) * ldx + off + e, g[e]);
+        }
+    }
+}
+
+template <typename I>
+__global__ void count_columns_kernel(const I *__restrict__ indices, int64_t num_edges, int32_t *__restrict__ count) {
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < num_edges;
+         e += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        atomicAdd(count + indices[e], 1);
+}
+
+template <typename I>
+__global__ void norm_scales_kernel(const I *__restrict__ indptr, const int32_t *__restrict__ col_count, int64_t rows,
+                                   int64_t cols, int norm, float *__restrict__ row_scale,
+                                   float *__restrict__ col_scale) {
+    const int64_t n = rows > cols ? rows : cols;
+    for (int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < n;
+         t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        if (t < rows) {
+            const float d = fmaxf(static_cast<float>(indptr[t + 1] - indptr[t]), 1.0f);
+            float s = 1.0f;
+            if (norm == TGNN_NORM_RIGHT) s = 1.0f / d;
+            if (norm == TGNN_NORM_BOTH) s = 1.0f / sqrtf(d);
+            row_scale[t] = s;
+        }
+        if (t < cols) {
+            float s = 1.0f;
+            if (norm == TGNN_NORM_LEFT || norm == TGNN_NORM_BOTH) {
+                const float d = fmaxf(static_cast<float>(col_count[t]), 1.0f);
+                s = norm == TGNN_NORM_LEFT ? 1.0f / d : 1.0f / sqrtf(d);
+            }
+            col_scale[t] = s;
+        }
+    }
+}
+
+int grid_for(int64_t work_items, int threads, int device) {
+    int64_t blocks = (work_items + threads - 1) / threads;
+    const int64_t cap = static_cast<int64_t>(sm_count(device)) * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return static_cast<int>(blocks);
+}
+
+}  // namespace
+
+size_t reduce_scratch_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_chunks, int64_t cols) {
+    const int per = dtype == TGNN_F32 ? 4 : 8;
+    const Geometry geo = make_geometry(cols, per, 1);
+    size_t words = static_cast<size_t>(geo.vpl) * per;
+    if (op == TGNN_OP_REDUCE_MINMAX) words *= (1 + itype_size(itype) / 4);
+    return static_cast<size_t>(num_chunks) * geo.slices * words * 32 * sizeof(uint32_t);
+}
+
+}  // namespace tgnn
+
+using namespace tgnn;
+
+extern "C" int32_t tgnn_segment_reduce_forward(const tgnn_segment_reduce_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_REQUIRE(a->reduce >= TGNN_REDUCE_MIN && a->reduce <= TGNN_REDUCE_MEAN, TGNN_ERR_INVALID_ARGUMENT,
+                 "reduce must be min, max, sum or mean (got %d)", a->reduce);
+    TGNN_TRY(check_reduce_io(a->exec, a->csr, a->sched, a->x, a->out));
+    if (a->csr.num_rows == 0) return TGNN_OK;
+    const bool minmax = a->reduce == TGNN_REDUCE_MIN || a->reduce == TGNN_REDUCE_MAX;
+    if (minmax && a->arg_idx != nullptr)
+        TGNN_REQUIRE(aligned16(a->arg_idx), TGNN_ERR_INVALID_ARGUMENT, "arg_idx is not 16-byte aligned");
+    const int per = a->x.dtype == TGNN_F32 ? 4 : 8;
+    const Geometry geo = make_geometry(a->x.cols, per, 1);
+    return dispatch_tiv(a->x.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
+        using T = typename decltype(tt)::type;
+        using I = typename decltype(it)::type;
+        constexpr int kVpl = decltype(vt)::value;
+        auto p = make_params<T, I>(a->x, a->out, minmax ? a->arg_idx : nullptr);
+        p.mean_by_degree = a->reduce == TGNN_REDUCE_MEAN;
+        switch (a->reduce) {
+            case TGNN_REDUCE_MIN:
+                return run_tiers<MinMaxOp<T, I, kVpl, false>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
+                                                              a->workspace_bytes, false);
+            case TGNN_REDUCE_MAX:
+                return run_tiers<MinMaxOp<T, I, kVpl, true>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
+                                                             a->workspace_bytes, false);
+            default:
+                return run_tiers<WeightedSumOp<T, I, kVpl, false>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
+                                                                   a->workspace_bytes, false);
+        }
+    });
+}
+
+extern "C" int32_t tgnn_segment_reduce_backward(const tgnn_segment_reduce_bwd_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));
+    TGNN_REQUIRE(a->itype == TGNN_I32 || a->itype == TGNN_I64, TGNN_ERR_INVALID_ARGUMENT, "unknown index type %d",
+                 a->itype);
+    TGNN_TRY(check_mat(a->grad_out, "grad_out", a->grad_out.rows, a->grad_out.cols, -1));
+    TGNN_TRY(check_mat(a->grad_x, "grad_x", a->grad_x.rows, a->grad_out.cols, a->grad_out.dtype));
+    TGNN_REQUIRE(a->arg_idx != nullptr || a->grad_out.rows == 0, TGNN_ERR_INVALID_ARGUMENT, "arg_idx is null");
+    cudaStream_t stream = static_cast<cudaStream_t>(a->exec.stream);
+    const size_t esz = dtype_size(a->grad_x.dtype);
+    if (a->grad_x.rows > 0) {
+        if (a->grad_x.row_stride == a->grad_x.cols) {
+            TGNN_CUDA(cudaMemsetAsync(a->grad_x.data, 0, static_cast<size_t>(a->grad_x.rows) * a->grad_x.cols * esz,
+                                      stream));
+        } else {
+            TGNN_CUDA(cudaMemset2DAsync(a->grad_x.data, a->grad_x.row_stride * esz, 0, a->grad_x.cols * esz,
+                                        a->grad_x.rows, stream));
+        }
+    }
+    if (a->grad_out.rows == 0) return TGNN_OK;
+    return dispatch_tiv(a->grad_out.dtype, a->itype, 1, [&](auto tt, auto it, auto) -> int32_t {
+        using T = typename decltype(tt)::type;
+        using I = typename decltype(it)::type;
+        const int64_t work = a->grad_out.rows * (a->grad_out.cols / Elem<T>::kPerChunk);
+        scatter_to_winner_kernel<T, I><<<grid_for(work, 256, a->exec.device), 256, 0, stream>>>(
+            static_cast<const T *>(a->grad_out.data), a->grad_out.row_stride, static_cast<const I *>(a->arg_idx),
+            static_cast<T *>(a->grad_x.data), a->grad_x.row_stride, a->grad_out.rows,
+            static_cast<int>(a->grad_out.cols));
+        TGNN_CUDA(cudaGetLastError());
+        return TGNN_OK;
+    });
+}
+
+extern "C" int32_t tgnn_degree_norm(const tgnn_degree_norm_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));
+    TGNN_TRY(check_csr(a->csr));
+    TGNN_REQUIRE(a->norm >= TGNN_NORM_NONE && a->norm <= TGNN_NORM_BOTH, TGNN_ERR_INVALID_ARGUMENT,
+                 "norm must be none, right, left or both (got %d)", a->norm);
+    TGNN_REQUIRE(a->row_scale != nullptr && a->col_scale != nullptr && a->col_count != nullptr,
+                 TGNN_ERR_INVALID_ARGUMENT, "scale or count buffer is null");
+    cudaStream_t stream = static_cast<cudaStream_t>(a->exec.stream);
+    const bool need_counts = a->norm == TGNN_NORM_LEFT || a->norm == TGNN_NORM_BOTH;
+    if (a->csr.num_cols > 0)
+        TGNN_CUDA(cudaMemsetAsync(a->col_count, 0, static_cast<size_t>(a->csr.num_cols) * sizeof(int32_t), stream));
+    const int64_t n = a->csr.num_rows > a->csr.num_cols ? a->csr.num_rows : a->csr.num_cols;
+    if (n == 0) return TGNN_OK;
+    auto body = [&](auto it) -> int32_t {
+        using I = typename decltype(it)::type;
+        if (need_counts && a->csr.num_edges > 0) {
+            count_columns_kernel<I><<<grid_for(a->csr.num_edges, 256, a->exec.device), 256, 0, stream>>>(
+                static_cast<const I *>(a->csr.indices), a->csr.num_edges, a->col_count);
+            TGNN_CUDA(cudaGetLastError());
+        }
+        norm_scales_kernel<I><<<grid_for(n, 256, a->exec.device), 256, 0, stream>>>(
+            static_cast<const I *>(a->csr.indptr), a->col_count, a->csr.num_rows, a->csr.num_cols, a->norm,
+            a->row_scale, a->col_scale);
+        TGNN_CUDA(cudaGetLastError());
+        return TGNN_OK;
+    };
+    return a->csr.itype == TGNN_I32 ? body(TypeTag<int32_t>{}) : body(TypeTag<int64_t>{});
+}
+
+extern "C" int32_t tgnn_spmm(const tgnn_spmm_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_reduce_io(a->exec, a->csr, a->sched, a->x, a->out));
+    if (a->csr.num_rows == 0) return TGNN_OK;
+    const int per = a->x.dtype == TGNN_F32 ? 4 : 8;
+    const Geometry geo = make_geometry(a->x.cols, per, 1);
+    const bool weighted = a->row_scale != nullptr || a->col_scale != nullptr || a->edge_weight != nullptr;
+    return dispatch_tiv(a->x.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
+        using T = typename decltype(tt)::type;
+        using I = typename decltype(it)::type;
+        constexpr int kVpl = decltype(vt)::value;
+        auto p = make_params<T, I>(a->x, a->out, nullptr);
+        p.row_scale = a->row_scale;
+        p.col_scale = a->col_scale;
+        p.edge_weight = a->edge_weight;
+        if (weighted)
+            return run_tiers<WeightedSumOp<T, I, kVpl, true>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
+                                                              a->workspace_bytes, false);
+        return run_tiers<WeightedSumOp<T, I, kVpl, false>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
+                                                           a->workspace_bytes, false);
+    });
+}

@@ -1,0 +1,151 @@
+// Shared device helpers: 128-bit feature-row IO with cache hints, element
+// conversion, warp-level primitives.  Everything here is SIMT; the path is
+// gather-bound, so there is no tensor-core code in this library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tgnn {
+
+constexpr int kWarp = 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+// ---- element traits ---------------------------------------------------------
+// A "chunk" is 16 bytes of a feature row: 4 fp32 or 8 half/bf16 values.
+
+template <typename T>
+struct Elem;
+
+template <>
+struct Elem<float> {
+    static constexpr int kPerChunk = 4;
+    __device__ static __forceinline__ void unpack(const uint4 &raw, float *f) {
+        f[0] = __uint_as_float(raw.x);
+        f[1] = __uint_as_float(raw.y);
+        f[2] = __uint_as_float(raw.z);
+        f[3] = __uint_as_float(raw.w);
+    }
+    __device__ static __forceinline__ uint4 pack(const float *f) {
+        return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+    }
+    __device__ static __forceinline__ float to_float(float v) { return v; }
+    __device__ static __forceinline__ float from_float(float v) { return v; }
+};
+
+template <>
+struct Elem<__half> {
+    static constexpr int kPerChunk = 8;
+    __device__ static __forceinline__ void unpack(const uint4 &raw, float *f) {
+        const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 t = __half22float2(h[i]);
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+        }
+    }
+    __device__ static __forceinline__ uint4 pack(const float *f) {
+        uint4 raw;
+        __half2 *h = reinterpret_cast<__half2 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        return raw;
+    }
+    __device__ static __forceinline__ float to_float(__half v) { return __half2float(v); }
+    __device__ static __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
+};
+
+template <>
+struct Elem<__nv_bfloat16> {
+    static constexpr int kPerChunk = 8;
+    __device__ static __forceinline__ void unpack(const uint4 &raw, float *f) {
+        // bf16 -> fp32 is a 16-bit shift of the bit pattern.
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    __device__ static __forceinline__ uint4 pack(const float *f) {
+        uint4 raw;
+        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        return raw;
+    }
+    __device__ static __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ static __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+};
+
+// ---- global memory access ------------------------------------------------------
+
+// L2 policy that keeps gathered source rows resident in preference to the
+// streamed traffic (indices, outputs): the per-load form of an L2 persistence
+// window, usable for rows that are not contiguous in memory.
+__device__ __forceinline__ uint64_t make_keep_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+// 16-byte gather of read-only data through the non-coherent path with an L2
+// eviction hint.  `p` must be 16-byte aligned.
+__device__ __forceinline__ uint4 ld_gather16(const void *p, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(policy));
+    return v;
+}
+
+// 16-byte read of data touched once (row-local operands): do not pollute L1.
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// 16-byte streaming store (outputs are written once and not re-read by the kernel).
+__device__ __forceinline__ void st_stream16(void *p, const uint4 &v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+template <typename I>
+__device__ __forceinline__ I ld_index(const I *p) {
+    return __ldg(p);
+}
+
+// ---- warp primitives -------------------------------------------------------------
+
+// Sum over aligned groups of `kLanes` consecutive lanes (power of two <= 32);
+// every lane of a group ends with the group's total.
+template <int kLanes>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+    for (int o = kLanes / 2; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+    return v;
+}
+
+__device__ __forceinline__ int64_t shfl_idx(int64_t v, int src) {
+    int lo = __shfl_sync(kFull, static_cast<int>(v & 0xffffffffll), src);
+    int hi = __shfl_sync(kFull, static_cast<int>(v >> 32), src);
+    return (static_cast<int64_t>(hi) << 32) | static_cast<uint32_t>(lo);
+}
+__device__ __forceinline__ int32_t shfl_idx(int32_t v, int src) { return __shfl_sync(kFull, v, src); }
+
+__device__ __forceinline__ uint32_t shfl_xor_word(uint32_t v, int mask) { return __shfl_xor_sync(kFull, v, mask); }
+
+__host__ __device__ constexpr int ilog2_ceil_pow2(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+}  // namespace tgnn

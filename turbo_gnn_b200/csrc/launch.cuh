@@ -1,0 +1,126 @@
+// Host-side launch helpers: error reporting, argument checks and the function
+// that runs one op over the three tiers of a schedule.
+#pragma once
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/tgnn_abi.h"
+#include "sweep.cuh"
+
+namespace tgnn {
+
+// Thread-local text of the last failure (read by tgnn_last_error).
+char *error_buffer();
+constexpr size_t kErrorBufferLen = 512;
+
+inline int32_t fail(tgnn_status code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error_buffer(), kErrorBufferLen, fmt, ap);
+    va_end(ap);
+    return static_cast<int32_t>(code);
+}
+
+#define TGNN_REQUIRE(cond, code, ...)                    \
+    do {                                                 \
+        if (!(cond)) return ::tgnn::fail(code, __VA_ARGS__); \
+    } while (0)
+
+#define TGNN_CUDA(expr)                                                                                    \
+    do {                                                                                                   \
+        cudaError_t err__ = (expr);                                                                        \
+        if (err__ != cudaSuccess)                                                                          \
+            return ::tgnn::fail(TGNN_ERR_CUDA, "%s failed: %s (%d)", #expr, cudaGetErrorString(err__),     \
+                                static_cast<int>(err__));                                                  \
+    } while (0)
+
+#define TGNN_TRY(expr)                    \
+    do {                                  \
+        int32_t st__ = (expr);            \
+        if (st__ != TGNN_OK) return st__; \
+    } while (0)
+
+inline size_t dtype_size(int32_t dt) { return dt == TGNN_F32 ? 4 : 2; }
+inline size_t itype_size(int32_t it) { return it == TGNN_I32 ? 4 : 8; }
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
+
+// Number of SMs of a device, cached per ordinal (read-only query).
+int sm_count(int device);
+
+int32_t check_exec(const tgnn_exec &e);
+int32_t check_csr(const tgnn_csr &c);
+int32_t check_schedule(const tgnn_schedule &s, const tgnn_csr &c);
+// Matrix usable with 128-bit row access: non-null (unless rows == 0), dtype
+// known, base and row pitch 16-byte aligned, cols a multiple of the chunk.
+int32_t check_mat(const tgnn_mat &m, const char *name, int64_t rows, int64_t cols, int32_t dtype);
+
+// Lane geometry for a feature row of `cols` elements of `chunk_elems` per
+// 16 bytes: chunks per lane (1,2,4,8), lanes per edge group and feature slices.
+struct Geometry {
+    int vpl;     // chunks per lane
+    int G;       // lanes per edge group
+    int slices;  // grid.y
+};
+Geometry make_geometry(int64_t cols, int chunk_elems, int min_group_lanes);
+
+template <class Op>
+size_t hub_scratch_bytes(int64_t num_chunks, int slices) {
+    return static_cast<size_t>(num_chunks) * slices * Op::kWords * 32 * sizeof(uint32_t);
+}
+
+// Runs `Op` over the light, heavy and hub tiers.  `persistent_light` caps the
+// light grid so that each warp visits many rows (ops with cross-row carry).
+template <class Op>
+int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_schedule &s, const tgnn_exec &ex,
+                  const Geometry &geo, void *scratch, size_t scratch_bytes, bool persistent_light) {
+    using I = typename Op::index_t;
+    cudaStream_t stream = static_cast<cudaStream_t>(ex.stream);
+    CsrDev<I> c{static_cast<const I *>(csr.indptr), static_cast<const I *>(csr.indices)};
+    const int carry_smem = Op::kCarryWords * 32 * static_cast<int>(sizeof(uint32_t));
+
+    if (s.num_light > 0) {
+        const int warps = s.light_warps;
+        int64_t blocks = (s.num_light + warps - 1) / warps;
+        if (persistent_light) {
+            const int64_t cap = static_cast<int64_t>(sm_count(ex.device)) * (2048 / (warps * 32)) ;
+            if (blocks > cap) blocks = cap;
+        }
+        dim3 grid(static_cast<unsigned>(blocks), geo.slices);
+        sweep_light_kernel<Op><<<grid, warps * 32, carry_smem * warps, stream>>>(
+            p, c, static_cast<const I *>(s.light_rows), s.num_light, geo.G);
+        TGNN_CUDA(cudaGetLastError());
+    }
+    HubDev<I> hub{static_cast<const I *>(s.hub_rows), s.hub_part_ptr, s.chunk_hub, s.chunk_edges};
+    const int hw = s.heavy_warps;
+    const size_t merge_smem = static_cast<size_t>(hw > 1 ? hw - 1 : 0) * Op::kWords * 32 * sizeof(uint32_t);
+    if (s.num_heavy > 0) {
+        dim3 grid(static_cast<unsigned>(s.num_heavy), geo.slices);
+        auto k = sweep_heavy_kernel<Op, false>;
+        if (merge_smem > 48 * 1024)
+            TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
+        k<<<grid, hw * 32, merge_smem, stream>>>(p, c, static_cast<const I *>(s.heavy_rows), hub, nullptr, geo.G);
+        TGNN_CUDA(cudaGetLastError());
+    }
+    if (s.num_hub > 0) {
+        const size_t need = hub_scratch_bytes<Op>(s.num_chunks, geo.slices);
+        TGNN_REQUIRE(scratch != nullptr && scratch_bytes >= need, TGNN_ERR_WORKSPACE,
+                     "hub tier needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+        TGNN_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, TGNN_ERR_WORKSPACE,
+                     "scratch must be 256-byte aligned");
+        uint32_t *partials = static_cast<uint32_t *>(scratch);
+        dim3 grid(static_cast<unsigned>(s.num_chunks), geo.slices);
+        auto k = sweep_heavy_kernel<Op, true>;
+        if (merge_smem > 48 * 1024)
+            TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
+        k<<<grid, hw * 32, merge_smem, stream>>>(p, c, nullptr, hub, partials, geo.G);
+        TGNN_CUDA(cudaGetLastError());
+        dim3 mgrid(static_cast<unsigned>((s.num_hub + 3) / 4), geo.slices);
+        hub_merge_kernel<Op><<<mgrid, 128, 0, stream>>>(p, c, hub, s.num_hub, partials, geo.G);
+        TGNN_CUDA(cudaGetLastError());
+    }
+    return TGNN_OK;
+}
+
+}  // namespace tgnn

@@ -1,0 +1,360 @@
+// Per-row ops of the fused GATv2 aggregation: forward, destination-side
+// backward (forward CSR) and source-side backward (transposed CSR).
+//
+//   z_ij = l_i + r_j          e_ij = sum_d a_d * LReLU(z_ijd)
+//   alpha_ij = softmax_j(e_ij)        out_i = sum_j alpha_ij r_j
+//   ge_ij = alpha_ij (<gh_i, r_j> - G_i),  G_i = <gh_i, out_i>
+//   grad_l_i = sum_j ge_ij LReLU'(z_ij) * a        grad_a += ge_ij LReLU(z_ij)
+//   grad_r_j = sum_i alpha_ij gh_i + ge_ij LReLU'(z_ij) * a
+// LReLU'(z) is 1 for z > 0 and the negative slope otherwise.
+#pragma once
+
+#include "ops_attn.cuh"
+
+namespace tgnn {
+
+template <typename T>
+struct Gatv2Params {
+    const T *l;
+    int64_t ldl;
+    const T *r;
+    int64_t ldr;
+    const T *attn;  // [H, D]
+    const T *gh;    // grad_out (backward only)
+    int64_t ldg;
+    const float *lse;  // [rows, H]
+    const float *G;    // [rows, H]
+    T *out;            // out (forward) | grad_l (bwd dst) | grad_r (bwd src)
+    int64_t ldo;
+    float *lse_out;      // forward
+    float *grad_attn;    // bwd dst, fp32 [H, D]
+    int cols;
+    int heads;
+    int head_dim;
+    float slope;
+};
+
+__device__ __forceinline__ float lrelu(float z, float slope) { return z > 0.0f ? z : z * slope; }
+__device__ __forceinline__ float lrelu_grad(float z, float slope) { return z > 0.0f ? 1.0f : slope; }
+
+// ---- forward ----------------------------------------------------------------------
+template <typename T, typename I, int kVpl>
+struct Gatv2FwdOp {
+    using index_t = I;
+    using Params = Gatv2Params<T>;
+    static constexpr int kPer = Elem<T>::kPerChunk;
+    static constexpr int kVals = kVpl * kPer;
+    using Acc = SoftmaxAcc<kVpl, kPer>;
+    static constexpr int kWords = Acc::kWords;
+    static constexpr int kUnroll = kVpl >= 4 ? 2 : 4;
+    static constexpr int kCarryWords = 0;
+
+    struct Row {
+        float l[kVals];
+    };
+    using State = Acc;
+    using Carry = NoCarry;
+    struct Frag {
+        uint4 raw[kVpl];
+    };
+
+    const Params &p;
+    const Lanes &L;
+    ChunkMap<kVpl, kPer> map;
+    HeadMap<kVpl, kPer> hm;
+    uint64_t keep;
+    float a[kVals];
+
+    __device__ __forceinline__ Gatv2FwdOp(const Params &p_, const Lanes &L_)
+        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {
+        load_row_f32<T, kVpl>(p.attn, map, a);
+    }
+    __device__ __forceinline__ void row_begin(I row, Row &rc) {
+        load_row_f32<T, kVpl>(p.l + static_cast<int64_t>(row) * p.ldl, map, rc.l);
+    }
+    __device__ __forceinline__ void init(State &s) { s.init(); }
+    __device__ __forceinline__ void load(I src, Frag &f) {
+        gather_row<T, kVpl>(p.r + static_cast<int64_t>(src) * p.ldr, map, keep, f.raw);
+    }
+    __device__ __forceinline__ void consume(const Row &rc, State &s, const Frag &f, I, I, bool valid) {
+        float pv[kVpl];
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            pv[v] = 0.0f;
+            if (valid && map.off[v] >= 0) {
+                float x[kPer];
+                Elem<T>::unpack(f.raw[v], x);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e)
+                    pv[v] = fmaf(a[v * kPer + e], lrelu(rc.l[v * kPer + e] + x[e], p.slope), pv[v]);
+            }
+        }
+        hm.finish(pv);
+        if (!valid) return;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+            float x[kPer];
+            Elem<T>::unpack(f.raw[v], x);
+            s.push(v, pv[v], x);
+        }
+    }
+    __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
+    __device__ __forceinline__ void to_words(const State &s, uint32_t *w) { s.to_words(w); }
+    __device__ __forceinline__ void from_words(State &s, const uint32_t *w) { s.from_words(w); }
+    __device__ __forceinline__ void row_end(I row, const Row &, State &s, I) {
+        if (L.grp != 0) return;
+        T *orow = p.out + static_cast<int64_t>(row) * p.ldo;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+            const float inv = s.s[v] > 0.0f ? 1.0f / s.s[v] : 0.0f;
+            float x[kPer];
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) x[e] = s.acc[v * kPer + e] * inv;
+            st_stream16(orow + map.off[v], Elem<T>::pack(x));
+            if (hm.writer[v])
+                p.lse_out[static_cast<int64_t>(row) * p.heads + hm.head[v]] =
+                    s.s[v] > 0.0f ? s.m[v] + __logf(s.s[v]) : -INFINITY;
+        }
+    }
+    __device__ __forceinline__ void flush_row(State &) {}
+    __device__ __forceinline__ void carry_init(Carry &) {}
+    __device__ __forceinline__ void carry_add(Carry &, const State &) {}
+    __device__ __forceinline__ void carry_flush(Carry &, uint32_t *) {}
+};
+
+// ---- backward, destination side (forward CSR) ------------------------------------------
+template <typename T, typename I, int kVpl>
+struct Gatv2BwdDstOp {
+    using index_t = I;
+    using Params = Gatv2Params<T>;
+    static constexpr int kPer = Elem<T>::kPerChunk;
+    static constexpr int kVals = kVpl * kPer;
+    static constexpr int kWords = 2 * kVals;  // grad_l | grad_a
+    static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
+    static constexpr int kCarryWords = kVals;
+
+    struct Row {
+        float l[kVals];
+        float gh[kVals];
+        float lse[kVpl];
+        float G[kVpl];
+    };
+    using State = SumAcc<2 * kVals>;
+    struct Carry {
+        float ga[kVals];
+    };
+    struct Frag {
+        uint4 raw[kVpl];
+    };
+
+    const Params &p;
+    const Lanes &L;
+    ChunkMap<kVpl, kPer> map;
+    HeadMap<kVpl, kPer> hm;
+    uint64_t keep;
+    float a[kVals];
+
+    __device__ __forceinline__ Gatv2BwdDstOp(const Params &p_, const Lanes &L_)
+        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {
+        load_row_f32<T, kVpl>(p.attn, map, a);
+    }
+    __device__ __forceinline__ void row_begin(I row, Row &rc) {
+        load_row_f32<T, kVpl>(p.l + static_cast<int64_t>(row) * p.ldl, map, rc.l);
+        load_row_f32<T, kVpl>(p.gh + static_cast<int64_t>(row) * p.ldg, map, rc.gh);
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            const int64_t at = static_cast<int64_t>(row) * p.heads + (hm.head[v] >= 0 ? hm.head[v] : 0);
+            rc.lse[v] = __ldg(p.lse + at);
+            rc.G[v] = __ldg(p.G + at);
+        }
+    }
+    __device__ __forceinline__ void init(State &s) { s.init(); }
+    __device__ __forceinline__ void load(I src, Frag &f) {
+        gather_row<T, kVpl>(p.r + static_cast<int64_t>(src) * p.ldr, map, keep, f.raw);
+    }
+    __device__ __forceinline__ void consume(const Row &rc, State &s, const Frag &f, I, I, bool valid) {
+        float pe[kVpl], pp[kVpl];
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            pe[v] = 0.0f;
+            pp[v] = 0.0f;
+            if (valid && map.off[v] >= 0) {
+                float x[kPer];
+                Elem<T>::unpack(f.raw[v], x);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    const int i = v * kPer + e;
+                    pe[v] = fmaf(a[i], lrelu(rc.l[i] + x[e], p.slope), pe[v]);
+                    pp[v] = fmaf(rc.gh[i], x[e], pp[v]);
+                }
+            }
+        }
+        hm.finish(pe);
+        hm.finish(pp);
+        if (!valid) return;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+            const float alpha = __expf(pe[v] - rc.lse[v]);
+            const float ge = alpha * (pp[v] - rc.G[v]);
+            float x[kPer];
+            Elem<T>::unpack(f.raw[v], x);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                const int i = v * kPer + e;
+                const float z = rc.l[i] + x[e];
+                s.a[i] = fmaf(ge * lrelu_grad(z, p.slope), a[i], s.a[i]);
+                s.a[kVals + i] = fmaf(ge, lrelu(z, p.slope), s.a[kVals + i]);
+            }
+        }
+    }
+    __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
+    __device__ __forceinline__ void to_words(const State &s, uint32_t *w) { s.to_words(w); }
+    __device__ __forceinline__ void from_words(State &s, const uint32_t *w) { s.from_words(w); }
+    __device__ __forceinline__ void row_end(I row, const Row &, State &s, I) {
+        if (L.grp != 0) return;
+        store_row_f32<T, kVpl>(p.out + static_cast<int64_t>(row) * p.ldo, map, s.a);
+    }
+    // Heavy / hub rows: the row's grad_a goes straight to global memory.
+    __device__ __forceinline__ void flush_row(State &s) {
+        if (L.grp != 0) return;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) atomicAdd(p.grad_attn + map.off[v] + e, s.a[kVals + v * kPer + e]);
+        }
+    }
+    // Light rows: grad_a rides in registers across the warp's rows, is summed over
+    // the CTA in shared memory and leaves with one atomic per feature per CTA.
+    __device__ __forceinline__ void carry_init(Carry &c) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) c.ga[i] = 0.0f;
+    }
+    __device__ __forceinline__ void carry_add(Carry &c, const State &s) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) c.ga[i] += s.a[kVals + i];
+    }
+    __device__ __forceinline__ void carry_flush(Carry &c, uint32_t *smem) {
+        float *buf = reinterpret_cast<float *>(smem);
+        const int warps = blockDim.x >> 5;
+        const int warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) buf[(warp * kVals + i) * 32 + L.lane] = c.ga[i];
+        __syncthreads();
+        if (warp != 0 || L.grp != 0) return;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                const int i = v * kPer + e;
+                float tot = 0.0f;
+                for (int w = 0; w < warps; ++w) tot += buf[(w * kVals + i) * 32 + L.lane];
+                atomicAdd(p.grad_attn + map.off[v] + e, tot);
+            }
+        }
+    }
+};
+
+// ---- backward, source side (transposed CSR: row = source j, column = destination i) -------
+template <typename T, typename I, int kVpl>
+struct Gatv2BwdSrcOp {
+    using index_t = I;
+    using Params = Gatv2Params<T>;
+    static constexpr int kPer = Elem<T>::kPerChunk;
+    static constexpr int kVals = kVpl * kPer;
+    static constexpr int kWords = kVals;
+    static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
+    static constexpr int kCarryWords = 0;
+
+    struct Row {
+        float r[kVals];
+    };
+    using State = SumAcc<kVals>;
+    using Carry = NoCarry;
+    struct Frag {
+        uint4 rawl[kVpl];
+        uint4 rawg[kVpl];
+        float lse[kVpl];
+        float G[kVpl];
+    };
+
+    const Params &p;
+    const Lanes &L;
+    ChunkMap<kVpl, kPer> map;
+    HeadMap<kVpl, kPer> hm;
+    uint64_t keep;
+    float a[kVals];
+
+    __device__ __forceinline__ Gatv2BwdSrcOp(const Params &p_, const Lanes &L_)
+        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {
+        load_row_f32<T, kVpl>(p.attn, map, a);
+    }
+    __device__ __forceinline__ void row_begin(I row, Row &rc) {
+        load_row_f32<T, kVpl>(p.r + static_cast<int64_t>(row) * p.ldr, map, rc.r);
+    }
+    __device__ __forceinline__ void init(State &s) { s.init(); }
+    __device__ __forceinline__ void load(I dst, Frag &f) {
+        gather_row<T, kVpl>(p.l + static_cast<int64_t>(dst) * p.ldl, map, keep, f.rawl);
+        gather_row<T, kVpl>(p.gh + static_cast<int64_t>(dst) * p.ldg, map, keep, f.rawg);
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            const int64_t at = static_cast<int64_t>(dst) * p.heads + (hm.head[v] >= 0 ? hm.head[v] : 0);
+            f.lse[v] = __ldg(p.lse + at);
+            f.G[v] = __ldg(p.G + at);
+        }
+    }
+    __device__ __forceinline__ void consume(const Row &rc, State &s, const Frag &f, I, I, bool valid) {
+        float pe[kVpl], pp[kVpl];
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            pe[v] = 0.0f;
+            pp[v] = 0.0f;
+            if (valid && map.off[v] >= 0) {
+                float xl[kPer], xg[kPer];
+                Elem<T>::unpack(f.rawl[v], xl);
+                Elem<T>::unpack(f.rawg[v], xg);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    const int i = v * kPer + e;
+                    pe[v] = fmaf(a[i], lrelu(xl[e] + rc.r[i], p.slope), pe[v]);
+                    pp[v] = fmaf(xg[e], rc.r[i], pp[v]);
+                }
+            }
+        }
+        hm.finish(pe);
+        hm.finish(pp);
+        if (!valid) return;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+            const float alpha = __expf(pe[v] - f.lse[v]);
+            const float ge = alpha * (pp[v] - f.G[v]);
+            float xl[kPer], xg[kPer];
+            Elem<T>::unpack(f.rawl[v], xl);
+            Elem<T>::unpack(f.rawg[v], xg);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                const int i = v * kPer + e;
+                const float z = xl[e] + rc.r[i];
+                s.a[i] = fmaf(alpha, xg[e], fmaf(ge * lrelu_grad(z, p.slope), a[i], s.a[i]));
+            }
+        }
+    }
+    __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
+    __device__ __forceinline__ void to_words(const State &s, uint32_t *w) { s.to_words(w); }
+    __device__ __forceinline__ void from_words(State &s, const uint32_t *w) { s.from_words(w); }
+    __device__ __forceinline__ void row_end(I row, const Row &, State &s, I) {
+        if (L.grp != 0) return;
+        store_row_f32<T, kVpl>(p.out + static_cast<int64_t>(row) * p.ldo, map, s.a);
+    }
+    __device__ __forceinline__ void flush_row(State &) {}
+    __device__ __forceinline__ void carry_init(Carry &) {}
+    __device__ __forceinline__ void carry_add(Carry &, const State &) {}
+    __device__ __forceinline__ void carry_flush(Carry &, uint32_t *) {}
+};
+
+}  // namespace tgnn

@@ -1,0 +1,280 @@
+// Per-row ops of the segment reductions: min/max with winner index, and the
+// weighted sum behind sum / mean / normalised SpMM.
+#pragma once
+
+#include "sweep.cuh"
+
+namespace tgnn {
+
+// Feature offset (in elements) of chunk v of this lane, or -1 when the chunk
+// lies beyond the row.
+template <int kVpl, int kPerChunk>
+struct ChunkMap {
+    int off[kVpl];
+    __device__ __forceinline__ ChunkMap(const Lanes &L, int cols) {
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            const int o = ((L.slice * kVpl + v) * L.G + L.g_lane) * kPerChunk;
+            off[v] = o < cols ? o : -1;
+        }
+    }
+};
+
+template <typename T, typename I>
+struct ReduceParams {
+    const T *x;
+    int64_t ldx;
+    T *out;
+    int64_t ldo;
+    I *arg;  // may be null
+    int cols;
+    // weighted sum only
+    const float *row_scale;
+    const float *col_scale;
+    const float *edge_weight;
+    int mean_by_degree;
+};
+
+// ---- min / max ------------------------------------------------------------------
+// Winner rule: strictly better value, or equal value and lower source id; a NaN
+// and the identity (+-inf) never win, so a row with no winner yields 0 / -1.
+template <typename T, typename I, int kVpl, bool kMax>
+struct MinMaxOp {
+    using index_t = I;
+    using Params = ReduceParams<T, I>;
+    static constexpr int kPer = Elem<T>::kPerChunk;
+    static constexpr int kVals = kVpl * kPer;
+    static constexpr int kIdxWords = sizeof(I) / 4;
+    static constexpr int kWords = kVals * (1 + kIdxWords);
+    static constexpr int kUnroll = (kVpl >= 4) ? 2 : 4;
+    static constexpr int kCarryWords = 0;
+
+    struct Row {};
+    struct Carry {};
+    struct State {
+        float val[kVals];
+        I idx[kVals];
+    };
+    struct Frag {
+        uint4 raw[kVpl];
+    };
+
+    const Params &p;
+    const Lanes &L;
+    ChunkMap<kVpl, kPer> map;
+    uint64_t keep;
+
+    __device__ __forceinline__ MinMaxOp(const Params &p_, const Lanes &L_)
+        : p(p_), L(L_), map(L_, p_.cols), keep(make_keep_policy()) {}
+
+    __device__ __forceinline__ static bool better(float a, float b) { return kMax ? (a > b) : (a < b); }
+
+    __device__ __forceinline__ void row_begin(I, Row &) {}
+    __device__ __forceinline__ void init(State &s) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) {
+            s.val[i] = kMax ? -INFINITY : INFINITY;
+            s.idx[i] = -1;
+        }
+    }
+    __device__ __forceinline__ void load(I src, Frag &f) {
+        const T *row = p.x + static_cast<int64_t>(src) * p.ldx;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v)
+            if (map.off[v] >= 0) f.raw[v] = ld_gather16(row + map.off[v], keep);
+    }
+    __device__ __forceinline__ void consume(const Row &, State &s, const Frag &f, I src, I, bool valid) {
+        if (!valid) return;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+            float x[kPer];
+            Elem<T>::unpack(f.raw[v], x);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                const int i = v * kPer + e;
+                const bool take = better(x[e], s.val[i]) || (x[e] == s.val[i] && src < s.idx[i]);
+                if (take) {
+                    s.val[i] = x[e];
+                    s.idx[i] = src;
+                }
+            }
+        }
+    }
+    __device__ __forceinline__ void merge(State &s, const State &o) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) {
+            const bool take = o.idx[i] >= 0 && (s.idx[i] < 0 || better(o.val[i], s.val[i]) ||
+                                                (o.val[i] == s.val[i] && o.idx[i] < s.idx[i]));
+            if (take) {
+                s.val[i] = o.val[i];
+                s.idx[i] = o.idx[i];
+            }
+        }
+    }
+    __device__ __forceinline__ void to_words(const State &s, uint32_t *w) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) {
+            w[i] = __float_as_uint(s.val[i]);
+            if (kIdxWords == 1) {
+                w[kVals + i] = static_cast<uint32_t>(s.idx[i]);
+            } else {
+                const uint64_t u = static_cast<uint64_t>(s.idx[i]);
+                w[kVals + 2 * i] = static_cast<uint32_t>(u);
+                w[kVals + 2 * i + 1] = static_cast<uint32_t>(u >> 32);
+            }
+        }
+    }
+    __device__ __forceinline__ void from_words(State &s, const uint32_t *w) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) {
+            s.val[i] = __uint_as_float(w[i]);
+            if (kIdxWords == 1) {
+                s.idx[i] = static_cast<I>(static_cast<int32_t>(w[kVals + i]));
+            } else {
+                const uint64_t u = static_cast<uint64_t>(w[kVals + 2 * i]) |
+                                   (static_cast<uint64_t>(w[kVals + 2 * i + 1]) << 32);
+                s.idx[i] = static_cast<I>(u);
+            }
+        }
+    }
+    __device__ __forceinline__ void row_end(I row, const Row &, State &s, I) {
+        if (L.grp != 0) return;
+        T *orow = p.out + static_cast<int64_t>(row) * p.ldo;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+            float x[kPer];
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) x[e] = s.idx[v * kPer + e] >= 0 ? s.val[v * kPer + e] : 0.0f;
+            st_stream16(orow + map.off[v], Elem<T>::pack(x));
+            if (p.arg != nullptr) {
+                I *arow = p.arg + static_cast<int64_t>(row) * p.cols + map.off[v];
+                constexpr int kPerStore = 16 / sizeof(I);
+#pragma unroll
+                for (int e = 0; e < kPer; e += kPerStore) {
+                    const I *ix = &s.idx[v * kPer + e];
+                    uint4 raw;
+                    if (kIdxWords == 1) {
+                        raw = make_uint4(static_cast<uint32_t>(ix[0]), static_cast<uint32_t>(ix[1]),
+                                         static_cast<uint32_t>(ix[2 % kPerStore]),
+                                         static_cast<uint32_t>(ix[3 % kPerStore]));
+                    } else {
+                        const uint64_t a = static_cast<uint64_t>(ix[0]);
+                        const uint64_t b = static_cast<uint64_t>(ix[1]);
+                        raw = make_uint4(static_cast<uint32_t>(a), static_cast<uint32_t>(a >> 32),
+                                         static_cast<uint32_t>(b), static_cast<uint32_t>(b >> 32));
+                    }
+                    st_stream16(arow + e, raw);
+                }
+            }
+        }
+    }
+    __device__ __forceinline__ void flush_row(State &) {}
+    __device__ __forceinline__ void carry_init(Carry &) {}
+    __device__ __forceinline__ void carry_add(Carry &, const State &) {}
+    __device__ __forceinline__ void carry_flush(Carry &, uint32_t *) {}
+};
+
+// ---- weighted sum -----------------------------------------------------------------
+// acc = sum_e w_e * x[src_e], w_e = col_scale[src] * edge_weight[e] (each
+// optional); row result = acc * row_scale[row], or acc / max(degree, 1).
+template <typename T, typename I, int kVpl, bool kWeighted>
+struct WeightedSumOp {
+    using index_t = I;
+    using Params = ReduceParams<T, I>;
+    static constexpr int kPer = Elem<T>::kPerChunk;
+    static constexpr int kVals = kVpl * kPer;
+    static constexpr int kWords = kVals;
+    static constexpr int kUnroll = (kVpl >= 4) ? 2 : 4;
+    static constexpr int kCarryWords = 0;
+
+    struct Row {};
+    struct Carry {};
+    struct State {
+        float acc[kVals];
+    };
+    struct Frag {
+        uint4 raw[kVpl];
+        float w;
+    };
+
+    const Params &p;
+    const Lanes &L;
+    ChunkMap<kVpl, kPer> map;
+    uint64_t keep;
+
+    __device__ __forceinline__ WeightedSumOp(const Params &p_, const Lanes &L_)
+        : p(p_), L(L_), map(L_, p_.cols), keep(make_keep_policy()) {}
+
+    __device__ __forceinline__ void row_begin(I, Row &) {}
+    __device__ __forceinline__ void init(State &s) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) s.acc[i] = 0.0f;
+    }
+    __device__ __forceinline__ void load(I src, Frag &f) {
+        const T *row = p.x + static_cast<int64_t>(src) * p.ldx;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v)
+            if (map.off[v] >= 0) f.raw[v] = ld_gather16(row + map.off[v], keep);
+        if (kWeighted) f.w = p.col_scale != nullptr ? __ldg(p.col_scale + src) : 1.0f;
+    }
+    __device__ __forceinline__ void consume(const Row &, State &s, const Frag &f, I, I eid, bool valid) {
+        if (!valid) return;
+        float w = 1.0f;
+        if (kWeighted) {
+            w = f.w;
+            if (p.edge_weight != nullptr) w *= __ldg(p.edge_weight + eid);
+        }
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+            float x[kPer];
+            Elem<T>::unpack(f.raw[v], x);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                if (kWeighted)
+                    s.acc[v * kPer + e] = fmaf(w, x[e], s.acc[v * kPer + e]);
+                else
+                    s.acc[v * kPer + e] += x[e];
+            }
+        }
+    }
+    __device__ __forceinline__ void merge(State &s, const State &o) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) s.acc[i] += o.acc[i];
+    }
+    __device__ __forceinline__ void to_words(const State &s, uint32_t *w) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) w[i] = __float_as_uint(s.acc[i]);
+    }
+    __device__ __forceinline__ void from_words(State &s, const uint32_t *w) {
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) s.acc[i] = __uint_as_float(w[i]);
+    }
+    __device__ __forceinline__ void row_end(I row, const Row &, State &s, I degree) {
+        if (L.grp != 0) return;
+        T *orow = p.out + static_cast<int64_t>(row) * p.ldo;
+        const float rs = p.row_scale != nullptr ? __ldg(p.row_scale + row) : 1.0f;
+        const float denom = p.mean_by_degree ? static_cast<float>(degree > 1 ? degree : 1) : 1.0f;
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
+            float x[kPer];
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                float a = s.acc[v * kPer + e];
+                if (p.mean_by_degree) a = a / denom;
+                if (kWeighted) a *= rs;
+                x[e] = a;
+            }
+            st_stream16(orow + map.off[v], Elem<T>::pack(x));
+        }
+    }
+    __device__ __forceinline__ void flush_row(State &) {}
+    __device__ __forceinline__ void carry_init(Carry &) {}
+    __device__ __forceinline__ void carry_add(Carry &, const State &) {}
+    __device__ __forceinline__ void carry_flush(Carry &, uint32_t *) {}
+};
+
+}  // namespace tgnn

@@ -1,0 +1,244 @@
+// Row-sweep skeleton shared by every aggregation op.
+//
+// An op describes WHAT happens per row and per edge (load the gathered rows,
+// fold them into a per-lane state, merge two states, write the row); this file
+// owns HOW rows are scheduled on the GPU:
+//
+//   light tier  one warp per row.  When a feature row needs fewer than 32
+//               16-byte chunks the warp splits into groups of G lanes that take
+//               different edges and merge at the end.  Grid-strided, so an op
+//               may carry accumulators across the rows a warp visits.
+//   heavy tier  one CTA per row; warps take 32-edge blocks round-robin and
+//               merge their states through shared memory.
+//   hub tier    one CTA per chunk of a hub row; the merged CTA state goes to
+//               scratch and a second kernel (one warp per hub row) merges the
+//               chunks and writes the row.
+//
+// Column indices are read once per warp as a coalesced 32-wide block, the next
+// block is prefetched into registers while the current one is processed, and
+// single indices are handed out by shuffle.
+#pragma once
+
+#include "common.cuh"
+
+namespace tgnn {
+
+template <typename I>
+struct CsrDev {
+    const I *indptr;
+    const I *indices;
+};
+
+template <typename I>
+struct HubDev {
+    const I *hub_rows;
+    const int32_t *part_ptr;
+    const int32_t *chunk_hub;
+    int32_t chunk_edges;
+};
+
+struct Lanes {
+    int lane;    // 0..31
+    int G;       // lanes per edge group (power of two)
+    int g_lane;  // lane % G
+    int grp;     // lane / G
+    int ngrp;    // 32 / G
+    int slice;   // feature slice of this warp (blockIdx.y)
+};
+
+__device__ __forceinline__ Lanes make_lanes(int G) {
+    Lanes L;
+    L.lane = threadIdx.x & 31;
+    L.G = G;
+    L.g_lane = L.lane & (G - 1);
+    L.grp = L.lane / G;
+    L.ngrp = 32 / G;
+    L.slice = blockIdx.y;
+    return L;
+}
+
+// Fold the edges [e0, e1) of one row into `st`; blocks of 32 edges are taken
+// with stride `stride_blocks` starting at block `first_block` (1/0 for a warp
+// that owns the whole row).
+template <class Op>
+__device__ __forceinline__ void sweep_edges(Op &op, const typename Op::Row &rc, typename Op::State &st,
+                                            const typename Op::index_t *__restrict__ indices, typename Op::index_t e0,
+                                            typename Op::index_t e1, int first_block, int stride_blocks,
+                                            const Lanes &L) {
+    using I = typename Op::index_t;
+    constexpr int U = Op::kUnroll;
+    const I step = static_cast<I>(stride_blocks) * 32;
+    I base = e0 + static_cast<I>(first_block) * 32;
+    I mine = 0;
+    if (base + L.lane < e1) mine = ld_index(indices + base + L.lane);
+    for (; base < e1; base += step) {
+        const I nbase = base + step;
+        I next = 0;
+        if (nbase + L.lane < e1) next = ld_index(indices + nbase + L.lane);  // prefetch
+        const I left = e1 - base;
+        const int cnt = left < 32 ? static_cast<int>(left) : 32;
+        for (int k = 0; k < cnt; k += L.ngrp * U) {
+            typename Op::Frag frag[U];
+            I src[U];
+            bool ok[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int slot = k + u * L.ngrp + L.grp;
+                ok[u] = slot < cnt;
+                src[u] = shfl_idx(mine, slot & 31);
+                if (ok[u]) op.load(src[u], frag[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int slot = k + u * L.ngrp + L.grp;
+                op.consume(rc, st, frag[u], src[u], base + slot, ok[u]);
+            }
+        }
+        mine = next;
+    }
+}
+
+// Merge the states of the edge groups of one warp into every lane.
+template <class Op>
+__device__ __forceinline__ void merge_groups(Op &op, typename Op::State &st, const Lanes &L) {
+    for (int o = L.G; o < 32; o <<= 1) {
+        uint32_t w[Op::kWords];
+        op.to_words(st, w);
+#pragma unroll
+        for (int i = 0; i < Op::kWords; ++i) w[i] = shfl_xor_word(w[i], o);
+        typename Op::State other;
+        op.from_words(other, w);
+        op.merge(st, other);
+    }
+}
+
+// ---- light tier ---------------------------------------------------------------
+template <class Op>
+__global__ void __launch_bounds__(256) sweep_light_kernel(typename Op::Params p, CsrDev<typename Op::index_t> csr,
+                                                          const typename Op::index_t *__restrict__ rows,
+                                                          int64_t n_rows, int G) {
+    using I = typename Op::index_t;
+    extern __shared__ __align__(16) uint32_t smem[];
+    const Lanes L = make_lanes(G);
+    const int warps = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5;
+    Op op(p, L);
+    typename Op::Carry carry;
+    op.carry_init(carry);
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * warps + warp; r < n_rows;
+         r += static_cast<int64_t>(gridDim.x) * warps) {
+        const I row = rows[r];
+        const I e0 = csr.indptr[row];
+        const I e1 = csr.indptr[row + 1];
+        typename Op::Row rc;
+        op.row_begin(row, rc);
+        typename Op::State st;
+        op.init(st);
+        sweep_edges(op, rc, st, csr.indices, e0, e1, 0, 1, L);
+        merge_groups(op, st, L);
+        op.row_end(row, rc, st, e1 - e0);
+        op.carry_add(carry, st);
+    }
+    op.carry_flush(carry, smem);
+}
+
+// ---- heavy and hub tiers --------------------------------------------------------
+// kPartial = false: blockIdx.x indexes `rows` (heavy tier), the CTA writes the row.
+// kPartial = true : blockIdx.x is a hub chunk; the merged state goes to `partials`
+//                   as [chunk][slice][word][lane].
+template <class Op, bool kPartial>
+__global__ void __launch_bounds__(512)
+    sweep_heavy_kernel(typename Op::Params p, CsrDev<typename Op::index_t> csr,
+                       const typename Op::index_t *__restrict__ rows, HubDev<typename Op::index_t> hub,
+                       uint32_t *__restrict__ partials, int G) {
+    using I = typename Op::index_t;
+    extern __shared__ __align__(16) uint32_t smem[];
+    const Lanes L = make_lanes(G);
+    const int warps = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5;
+    I row, e0, e1;
+    if (kPartial) {
+        const int c = blockIdx.x;
+        const int k = hub.chunk_hub[c];
+        row = hub.hub_rows[k];
+        const I rb = csr.indptr[row];
+        const I re = csr.indptr[row + 1];
+        e0 = rb + static_cast<I>(c - hub.part_ptr[k]) * hub.chunk_edges;
+        e1 = e0 + hub.chunk_edges;
+        if (e1 > re) e1 = re;
+    } else {
+        row = rows[blockIdx.x];
+        e0 = csr.indptr[row];
+        e1 = csr.indptr[row + 1];
+    }
+    Op op(p, L);
+    typename Op::Row rc;
+    op.row_begin(row, rc);
+    typename Op::State st;
+    op.init(st);
+    sweep_edges(op, rc, st, csr.indices, e0, e1, warp, warps, L);
+    merge_groups(op, st, L);
+
+    // Cross-warp merge: warps 1.. spill, warp 0 folds them in order.
+    uint32_t w[Op::kWords];
+    if (warp > 0) {
+        op.to_words(st, w);
+        uint32_t *dst = smem + static_cast<size_t>(warp - 1) * Op::kWords * 32;
+#pragma unroll
+        for (int i = 0; i < Op::kWords; ++i) dst[i * 32 + L.lane] = w[i];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        for (int o = 1; o < warps; ++o) {
+            const uint32_t *src = smem + static_cast<size_t>(o - 1) * Op::kWords * 32;
+#pragma unroll
+            for (int i = 0; i < Op::kWords; ++i) w[i] = src[i * 32 + L.lane];
+            typename Op::State other;
+            op.from_words(other, w);
+            op.merge(st, other);
+        }
+        if (kPartial) {
+            op.to_words(st, w);
+            uint32_t *dst =
+                partials + (static_cast<size_t>(blockIdx.x) * gridDim.y + blockIdx.y) * Op::kWords * 32;
+#pragma unroll
+            for (int i = 0; i < Op::kWords; ++i) dst[i * 32 + L.lane] = w[i];
+        } else {
+            op.row_end(row, rc, st, e1 - e0);
+            op.flush_row(st);
+        }
+    }
+}
+
+// Second pass of the hub tier: one warp per (hub row, slice) folds the row's
+// chunk states in chunk order and writes the row.
+template <class Op>
+__global__ void __launch_bounds__(128) hub_merge_kernel(typename Op::Params p, CsrDev<typename Op::index_t> csr,
+                                                        HubDev<typename Op::index_t> hub, int64_t n_hub,
+                                                        const uint32_t *__restrict__ partials, int G) {
+    using I = typename Op::index_t;
+    const Lanes L = make_lanes(G);
+    const int64_t k = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (k >= n_hub) return;
+    const I row = hub.hub_rows[k];
+    Op op(p, L);
+    typename Op::Row rc;
+    op.row_begin(row, rc);
+    typename Op::State st;
+    op.init(st);
+    const int c0 = hub.part_ptr[k];
+    const int c1 = hub.part_ptr[k + 1];
+    for (int c = c0; c < c1; ++c) {
+        const uint32_t *src = partials + (static_cast<size_t>(c) * gridDim.y + blockIdx.y) * Op::kWords * 32;
+        uint32_t w[Op::kWords];
+#pragma unroll
+        for (int i = 0; i < Op::kWords; ++i) w[i] = src[i * 32 + L.lane];
+        typename Op::State other;
+        op.from_words(other, w);
+        op.merge(st, other);
+    }
+    op.row_end(row, rc, st, csr.indptr[row + 1] - csr.indptr[row]);
+    op.flush_row(st);
+}
+
+}  // namespace tgnn
