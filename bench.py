@@ -1,0 +1,493 @@
+#!/usr/bin/env python
+"""Benchmark of the aggregation hot path: aggregated edges/s (forward + backward) on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0..cfg3] [--shrink f]
+    python bench.py --impl reference ...      # the CPU scatter path on the host cores
+
+A step is one forward + backward pass of the workload's op over the whole (or, with N > 1, the
+row-partitioned) synthetic graph.  The default workload is cfg2: fused graph-transformer
+attention on a 232 965-node / ~114 M-edge power-law graph, the first of the workloads that is
+specified for 1/2/4/8 GPUs.  One JSON line is printed by rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {"cfg0": 0, "cfg1": 1, "cfg2": 2, "cfg3": 3}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--shrink", type=float, default=1.0, help="scale nodes/edges down (tests, profiler captures)")
+    ap.add_argument("--quantile", type=float, default=0.99, help="light/heavy degree quantile of the graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cpu-sample-edges", type=int, default=400_000)
+    return ap.parse_args()
+
+
+# ---- environment ----------------------------------------------------------------------------
+
+
+def init_ranks(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return rank, world, local
+
+
+def measured_hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except (OSError, ValueError, KeyError):
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs (read-only)."""
+
+    _REASONS = {
+        0x4: "sw_power_cap",
+        0x8: "hw_slowdown",
+        0x20: "sw_thermal_slowdown",
+        0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index: int, period_s: float = 0.05):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+
+    def __enter__(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        except Exception:  # NVML missing: report nulls rather than fail the bench
+            self._thread = None
+        return self
+
+    def _loop(self):
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self._REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        return False
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": []}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ---- workloads -------------------------------------------------------------------------------
+
+
+class Job:
+    """One workload bound to this rank: a `step()` (forward + backward on device-resident inputs),
+    the host<->device tensors of the end-to-end variant and the byte model of each library call."""
+
+    def __init__(self, args, rank, world):
+        from turbo_gnn_b200 import dist as tdist
+        from turbo_gnn_b200 import synthetic
+
+        self.args, self.rank, self.world = args, rank, world
+        dev = torch.device("cuda", torch.cuda.current_device())
+        wl = synthetic.make_workload(WORKLOADS[args.workload], device=dev, shrink=args.shrink,
+                                     quantile=args.quantile)
+        self.wl = wl
+        self.op = wl.op
+        self.total_edges = wl.num_edges
+        self.num_nodes = wl.num_nodes
+        self.shard = None
+        graph = wl.graph
+        if world > 1:
+            self.shard = tdist.shard_graph(graph, rank, world, quantile=args.quantile)
+            graph = self.shard.graph
+        self.graph = graph
+        self.local_edges = graph.forward_indices.numel()
+        self.local_rows = graph.forward_indptr.numel() - 1
+        pick = (lambda t: self.shard.local_rows(t).contiguous()) if self.shard else (lambda t: t)
+        t = wl.tensors
+        if self.op == "gt":
+            self.inputs = [pick(t["Q"]), pick(t["K"]), pick(t["V"])]
+            self.grad = pick(t["grad"])
+        elif self.op == "gatv2":
+            self.inputs = [pick(t["x"]), pick(t["x_neighbors"]), t["attention_weights"]]
+            self.grad = pick(t["grad"])
+        elif self.op == "spmm":
+            self.inputs = [pick(t["x"])]
+            self.grad = pick(t["grad"])
+            self.scales = tdist.sharded_norm_scales(self.shard, "none") if self.shard else None
+        elif self.op == "reduce":
+            self.inputs = [pick(t["x"])]
+            self.grad = None
+        for x in self.inputs:
+            x.requires_grad_(self.op != "reduce")
+        if self.shard is not None:
+            del wl.tensors, wl.graph  # the full graph is not needed after sharding
+            self.wl.edge_index = None
+            torch.cuda.empty_cache()
+
+    # forward + backward on whatever `inputs` / `grad` currently hold
+    def step(self):
+        import turbo_gnn_b200 as tg
+        from turbo_gnn_b200 import dist as tdist
+
+        g, x = self.graph, self.inputs
+        if self.op == "gt":
+            if self.shard:
+                out = tdist.sharded_graph_transformer_aggr(self.shard, x[0], x[1], x[2], self.wl.params["scale"])
+            else:
+                out = tg.graph_transformer_aggr(g, None, x[0], x[1], x[2], self.wl.params["scale"])
+            return (out,) + torch.autograd.grad(out, x, self.grad)
+        if self.op == "gatv2":
+            if self.shard:
+                out = tdist.sharded_gatv2_aggr(self.shard, x[0], x[1], x[2], 0.2)
+            else:
+                out = tg.gatv2_aggr(g, x[0], x[1], x[2], 0.2)
+            return (out,) + torch.autograd.grad(out, x, self.grad)
+        if self.op == "spmm":
+            if self.shard:
+                out = tdist.sharded_spmm_aggr(self.shard, x[0], "none", self.scales)
+            else:
+                out = tg.spmm_aggr(x[0], g.forward_indptr, g.forward_indices, "none", -1, 256)
+            return (out,) + torch.autograd.grad(out, x, self.grad)
+        outs = []
+        for red in ("min", "max", "sum", "mean"):  # cfg0: forward only, four reductions
+            outs.append(tg.reduction_aggr(g, x[0], reduce=red))
+        return tuple(outs)
+
+    # ---- byte model (algorithmic bytes of one call of each library entry point, this rank) ----
+    def entry_bytes(self):
+        E, R = self.local_edges, self.local_rows
+        i = self.graph.forward_indptr.element_size()
+        x0 = self.inputs[0]
+        s = x0.element_size()
+        if self.op in ("gt", "gatv2"):
+            H = x0.shape[1]
+            F = x0.shape[1] * x0.shape[2]
+        else:
+            H, F = 1, x0.shape[1]
+        Fs = F * s
+        if self.op == "gt":
+            return {
+                "tgnn_gt_forward": E * (2 * Fs + i) + R * (2 * Fs + 4 * H),
+                "tgnn_gt_backward_dst": E * (2 * Fs + i) + R * (3 * Fs + 8 * H),
+                "tgnn_gt_backward_src": E * (2 * Fs + i + 8 * H) + R * (4 * Fs),
+                "tgnn_head_dot": R * (2 * Fs + 4 * H),
+            }
+        if self.op == "gatv2":
+            return {
+                "tgnn_gatv2_forward": E * (Fs + i) + R * (2 * Fs + 4 * H),
+                "tgnn_gatv2_backward_dst": E * (Fs + i) + R * (3 * Fs + 8 * H),
+                "tgnn_gatv2_backward_src": E * (2 * Fs + i + 8 * H) + R * (2 * Fs),
+                "tgnn_head_dot": R * (2 * Fs + 4 * H),
+            }
+        if self.op == "spmm":
+            return {"tgnn_spmm": E * (Fs + i) + R * (Fs + i)}
+        return {"tgnn_segment_reduce_forward": E * (Fs + i) + R * (Fs + i)}
+
+
+def timed_steps(fn, steps, world):
+    """Device time of `steps` calls of fn (ms): CUDA events on the current stream, max over ranks."""
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+# ---- CPU arm -----------------------------------------------------------------------------------
+
+
+def cpu_sample(job_cfg: int, shrink: float, sample_edges: int):
+    """A bounded sample of the workload for the host: the first destination rows holding about
+    `sample_edges` edges, with every source row they touch."""
+    from turbo_gnn_b200 import synthetic
+
+    # The graph is generated where that is fast (the GPU when there is one); only the sample and
+    # the feature tensors come to the host.
+    where = "cuda" if torch.cuda.is_available() else "cpu"
+    wl = synthetic.make_workload(job_cfg, device=where, shrink=shrink)
+    g = wl.graph
+    ptr = g.forward_indptr.long().cpu()
+    rows = int(torch.searchsorted(ptr, torch.tensor(sample_edges)).item())
+    rows = max(1, min(rows, wl.num_nodes))
+    e = int(ptr[rows].item())
+    dst = torch.repeat_interleave(torch.arange(rows), (ptr[1: rows + 1] - ptr[:rows]))
+    src = g.forward_indices[:e].long().cpu()
+    wl.tensors = {k: v.cpu() for k, v in wl.tensors.items()}
+    wl.graph, wl.edge_index = None, None
+    if where == "cuda":
+        torch.cuda.empty_cache()
+    return wl, torch.stack([src, dst]), rows, e
+
+
+def cpu_step_fn(wl, ei, rows):
+    from oracle import scatter_oracle as O
+
+    n = wl.num_nodes
+    t = wl.tensors
+    if wl.op == "gt":
+        q, k, v = (t[name].clone().requires_grad_() for name in ("Q", "K", "V"))
+        grad = t["grad"]
+
+        def fn():
+            out = O.gt_aggregate(q, k, v, ei, n, wl.params["scale"])
+            return torch.autograd.grad(out, (q, k, v), grad)
+
+    elif wl.op == "gatv2":
+        l, r, a = (t[name].clone().requires_grad_() for name in ("x", "x_neighbors", "attention_weights"))
+        grad = t["grad"]
+
+        def fn():
+            out = O.gatv2_aggregate(l, r, a, ei, n, 0.2)
+            return torch.autograd.grad(out, (l, r, a), grad)
+
+    elif wl.op == "spmm":
+        x = t["x"].float().clone().requires_grad_()
+        grad = t["grad"].float()
+
+        def fn():
+            out = O.spmm(x, ei, n, "none")
+            return torch.autograd.grad(out, (x,), grad)
+
+    else:
+        x = t["x"]
+
+        def fn():
+            return [O.segment_reduce(x, ei, n, red) for red in ("min", "max", "sum", "mean")]
+
+    return fn
+
+
+def run_cpu(args, steps, warmup):
+    """Edges/s of the CPU scatter path on the host cores over a bounded sample."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    wl, ei, rows, e = cpu_sample(WORKLOADS[args.workload], args.shrink, args.cpu_sample_edges)
+    fn = cpu_step_fn(wl, ei, rows)
+    for _ in range(warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return {
+        "value": e / dt,
+        "unit": "edges/s",
+        "cores": cores,
+        "kind": "port",
+        "sample": f"first {rows} destination rows ({e} edges) of {wl.name}, torch scatter ops, fwd+bwd",
+        "ms_per_step": dt * 1e3,
+    }
+
+
+def config_of(args, job=None):
+    cfg = {"workload": args.workload, "shrink": args.shrink, "l2": "inputs larger than L2 (no flush)"}
+    if job is not None:
+        cfg.update({"nodes": job.num_nodes, "edges": job.total_edges, "index_dtype": "int32",
+                    "quantile": args.quantile, "op": job.op,
+                    "parallelism": f"row-partition x{job.world}" if job.world > 1 else "single"})
+    return cfg
+
+
+def main_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    res = run_cpu(args, max(args.steps, 1), min(args.warmup, 1))
+    line = {
+        "impl": "reference",
+        "metric": "aggregated edges/s fwd+bwd",
+        "value": res["value"],
+        "unit": "edges/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": res["ms_per_step"],
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic",
+        "config": config_of(args),
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main_ours(args):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
+    rank, world, local = init_ranks(args.gpus)
+    from turbo_gnn_b200 import _abi
+
+    job = Job(args, rank, world)
+    for _ in range(max(args.warmup, 3)):
+        job.step()
+    with ClockSampler(local) as clocks:
+        ms = timed_steps(job.step, args.steps, world)
+    ms_step = ms / args.steps
+    value = job.total_edges / (ms_step * 1e-3)
+
+    # per-entry-point device time, same loop with events around each library call
+    _abi.trace.reset(True)
+    timed_steps(job.step, args.steps, world)
+    per_call = _abi.trace.mean_ms()
+    launches = _abi.trace.kernel_launches
+    _abi.trace.reset(False)
+    model = job.entry_bytes()
+    top = max((k for k in per_call if k in model), key=lambda k: per_call[k])
+    peak, peak_kind = measured_hbm_peak()
+    achieved = model[top] / (per_call[top] * 1e-3) / 1e9
+    traffic = None
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as fh:
+            rec = json.load(fh).get(f"{args.workload}:{top}")
+            if rec and args.shrink == 1.0 and world == 1:
+                traffic = rec["bytes_per_edge"] * job.local_edges
+    except (OSError, ValueError):
+        pass
+    step_bytes = sum(model[k] for k in per_call if k in model)
+    roofline = {
+        "bound": "hbm",
+        "kernel": top,
+        "achieved": achieved,
+        "peak": peak,
+        "peak_kind": peak_kind,
+        "unit": "GB/s",
+        "frac": achieved / peak,
+        "traffic": traffic,
+        "ms_per_call": per_call,
+        "step_algorithmic_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+    }
+
+    # end to end: host buffers in, host buffers out, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        host_in = [x.detach().cpu().pin_memory() for x in job.inputs]
+        host_grad = job.grad.cpu().pin_memory() if job.grad is not None else None
+        outs = job.step()
+        host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        h2d = sum(h.numel() * h.element_size() for h in host_in) + (
+            host_grad.numel() * host_grad.element_size() if host_grad is not None else 0)
+        d2h = sum(h.numel() * h.element_size() for h in host_out)
+
+        def e2e_step():
+            with torch.no_grad():
+                for dev_t, h in zip(job.inputs, host_in):
+                    dev_t.copy_(h, non_blocking=True)
+                if host_grad is not None:
+                    job.grad.copy_(host_grad, non_blocking=True)
+            res = job.step()
+            for h, o in zip(host_out, res):
+                h.copy_(o, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        e2e_ms = timed_steps(e2e_step, args.steps, world) / args.steps
+        e2e = {"value": job.total_edges / (e2e_ms * 1e-3), "unit": "edges/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        res = run_cpu(args, 2, 1)
+        cpu = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        x0 = job.inputs[0]
+        line = {
+            "metric": "aggregated edges/s fwd+bwd",
+            "value": value,
+            "unit": "edges/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step,
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}[x0.dtype],
+            "data": "synthetic",
+            "config": config_of(args, job),
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": launches,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    ns = parse_args()
+    sys.exit(main_reference(ns) if ns.impl == "reference" else main_ours(ns))

@@ -425,6 +425,8 @@ def compute_degrees(indptr, indices, in_degrees, out_degrees, block_dim=256):
     in_degrees.copy_(sp[1:] - sp[:-1])
 
 
+
+
 # ---------------------------------------------------------------------------------------
 # attention: shared host logic
 # ---------------------------------------------------------------------------------------
@@ -469,16 +471,19 @@ def _check_attention_inputs(*tensors):
         raise RuntimeError("attention operands must be float32/float16/bfloat16")
 
 
-def _head_dot(a: torch.Tensor, b: torch.Tensor, heads: int, head_dim: int) -> torch.Tensor:
-    dot = torch.empty((a.shape[0], heads), dtype=torch.float32, device=a.device)
-    args = _abi.HeadDotArgs(exec=_abi.exec_of(a), a=_abi.mat_of(a), b=_abi.mat_of(b), heads=heads,
-                            head_dim=head_dim, dot=_abi.ptr(dot))
-    _abi.call("tgnn_head_dot", args)
+def head_dot(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """fp32 [N, H]: per-head dot product of two [N, H, D] tensors (D already a supported size)."""
+    n, heads, dp = a.shape
+    dot = torch.empty((n, heads), dtype=torch.float32, device=a.device)
+    if n > 0:
+        args = _abi.HeadDotArgs(exec=_abi.exec_of(a), a=_abi.mat_of(a), b=_abi.mat_of(b), heads=heads, head_dim=dp,
+                                dot=_abi.ptr(dot))
+        _abi.call("tgnn_head_dot", args)
     return dot
 
 
-def _default_buckets(indptr):
-    return _bucket(indptr)
+def _strip(t: torch.Tensor, d: int) -> torch.Tensor:
+    return t if t.shape[-1] == d else t[..., :d].contiguous()
 
 
 # ---------------------------------------------------------------------------------------
@@ -490,9 +495,10 @@ def gatv2_forward(l, r, row_ptr, col_idx, attn_vec, negative_slope, light_nodes,
                   light_warps_per_block=1, heavy_warps_per_block=8):
     """``[h_out [N,H,D], logsumexp [N,H] fp32]`` (``csrc/turbo_gnn.cpp:21-25``).
 
-    ``l`` is the destination-side and ``r`` the source-side projection.  Head dims other than
-    16/32/64/128/256 are zero-padded (features and attention vector), which leaves scores and
-    outputs unchanged.
+    ``l`` is the destination-side projection (one row per CSR row), ``r`` the source-side one (one
+    row per CSR column; the two row counts may differ, as on a row shard of a partitioned graph).
+    Head dims other than 16/32/64/128/256 are zero-padded (features and attention vector), which
+    leaves scores and outputs unchanged.
     """
     _check_attention_inputs(l, r, attn_vec)
     _check_index_family(row_ptr, col_idx, light_nodes, heavy_nodes)
@@ -524,49 +530,30 @@ def gatv2_forward(l, r, row_ptr, col_idx, attn_vec, negative_slope, light_nodes,
             workspace_bytes=ws_bytes,
         )
         _abi.call("tgnn_gatv2_forward", args)
-    if dp != d:
-        out = out[..., :d].contiguous()
-    return [out, lse]
+    return [_strip(out, d), lse]
 
 
-def gatv2_backward(grad_h, l, r, row_ptr, col_idx, row_ptr_T, col_idx_T, attn_vec, logsumexp, negative_slope,
-                   grad_A_reduce_row_chunk_size, fwd_light_nodes, fwd_heavy_nodes, bwd_light_nodes, bwd_heavy_nodes,
-                   light_warps_per_block=1, heavy_warps_per_block=8, is_directed=True, out=None):
-    """``[grad_l, grad_r, grad_attn]`` (``csrc/turbo_gnn.cpp:27-33``).
+def gatv2_backward_dst(grad_h, l, r, row_ptr, col_idx, attn_vec, lse, G, negative_slope, light_nodes, heavy_nodes,
+                       light_warps=1, heavy_warps=8, grad_attn_f32=None):
+    """Destination-side pass over the forward CSR: ``(grad_l, grad_attn_f32 [H, Dp])``.
 
-    Two passes: destination side over the forward CSR (grad_l, grad_attn), source side over the
-    transposed CSR (grad_r).  ``is_directed=False`` means the caller aliased the transposed CSR to
-    the forward one; the same two passes run on it.  ``grad_A_reduce_row_chunk_size`` belonged to a
-    separate reduction kernel of the reference and is validated only.
+    ``grad_h``, ``l``, ``lse``, ``G`` have one row per CSR row; ``r`` one row per CSR column.
+    Gradients of the attention vector are ADDED into ``grad_attn_f32`` (created zeroed if absent).
     """
-    if grad_A_reduce_row_chunk_size not in (32, 64, 128, 256, 512, 1024, 2048):
-        raise RuntimeError("Wrong int value")
-    _check_attention_inputs(l, r, attn_vec, grad_h)
-    _check_index_family(row_ptr, col_idx, row_ptr_T, col_idx_T, fwd_light_nodes, fwd_heavy_nodes, bwd_light_nodes,
-                        bwd_heavy_nodes)
     n_rows, heads, d = l.shape
-    n_src = r.shape[0]
-    lw, hw = _clamp_light(light_warps_per_block), _clamp_heavy(heavy_warps_per_block)
     dp = _padded_head_dim(d)
-    if out is None:
-        out = gatv2_forward(l, r, row_ptr, col_idx, attn_vec, negative_slope, fwd_light_nodes, fwd_heavy_nodes)[0]
-    l_in, r_in = _head_rows(l, dp), _head_rows(r, dp)
-    g_in, o_in = _head_rows(grad_h.reshape(n_rows, heads, d), dp), _head_rows(out.reshape(n_rows, heads, d), dp)
+    l_in, r_in, g_in = _head_rows(l, dp), _head_rows(r, dp), _head_rows(grad_h, dp)
     a_in = _pad_cols(attn_vec, dp).contiguous()
-    lse = logsumexp.contiguous()
     grad_l = torch.empty((n_rows, heads, dp), dtype=l.dtype, device=l.device)
-    grad_r = torch.empty((n_src, heads, dp), dtype=l.dtype, device=l.device)
-    grad_a32 = torch.zeros((heads, dp), dtype=torch.float32, device=l.device)
+    if grad_attn_f32 is None:
+        grad_attn_f32 = torch.zeros((heads, dp), dtype=torch.float32, device=l.device)
     if n_rows > 0:
-        G = _head_dot(g_in, o_in, heads, dp)
-        ex = _abi.exec_of(l_in)
-        cols = heads * dp
-        f_sched = _sched(row_ptr, fwd_light_nodes, fwd_heavy_nodes)
-        ws, ws_bytes = _scratch(_abi.OP_GATV2_BWD_DST, f_sched, l_in, row_ptr.dtype, cols)
-        dst_args = _abi.Gatv2BwdDstArgs(
-            exec=ex,
-            csr=_abi.csr_of(row_ptr, col_idx, n_src),
-            sched=f_sched.to_struct(lw, hw),
+        sched = _sched(row_ptr, light_nodes, heavy_nodes)
+        ws, ws_bytes = _scratch(_abi.OP_GATV2_BWD_DST, sched, l_in, row_ptr.dtype, heads * dp)
+        args = _abi.Gatv2BwdDstArgs(
+            exec=_abi.exec_of(l_in),
+            csr=_abi.csr_of(row_ptr, col_idx, r.shape[0]),
+            sched=sched.to_struct(_clamp_light(light_warps), _clamp_heavy(heavy_warps)),
             grad_out=_abi.mat_of(g_in),
             l=_abi.mat_of(l_in),
             r=_abi.mat_of(r_in),
@@ -577,17 +564,33 @@ def gatv2_backward(grad_h, l, r, row_ptr, col_idx, row_ptr_T, col_idx_T, attn_ve
             head_dim=dp,
             negative_slope=float(negative_slope),
             grad_l=_abi.mat_of(grad_l),
-            grad_attn_f32=_abi.ptr(grad_a32),
+            grad_attn_f32=_abi.ptr(grad_attn_f32),
             workspace=_abi.ptr(ws),
             workspace_bytes=ws_bytes,
         )
-        _abi.call("tgnn_gatv2_backward_dst", dst_args)
-        b_sched = _sched(row_ptr_T, bwd_light_nodes, bwd_heavy_nodes)
-        ws2, ws2_bytes = _scratch(_abi.OP_GATV2_BWD_SRC, b_sched, l_in, row_ptr.dtype, cols)
-        src_args = _abi.Gatv2BwdSrcArgs(
-            exec=ex,
-            csr_t=_abi.csr_of(row_ptr_T, col_idx_T, n_rows),
-            sched=b_sched.to_struct(lw, hw),
+        _abi.call("tgnn_gatv2_backward_dst", args)
+    return _strip(grad_l, d), grad_attn_f32
+
+
+def gatv2_backward_src(grad_h, l, r, row_ptr_T, col_idx_T, attn_vec, lse, G, negative_slope, light_nodes,
+                       heavy_nodes, light_warps=1, heavy_warps=8):
+    """Source-side pass over the transposed CSR: ``grad_r``.
+
+    ``r`` has one row per row of the transposed CSR; ``grad_h``, ``l``, ``lse``, ``G`` one row per
+    column of it (the destination nodes).
+    """
+    n_src, heads, d = r.shape
+    dp = _padded_head_dim(d)
+    l_in, r_in, g_in = _head_rows(l, dp), _head_rows(r, dp), _head_rows(grad_h, dp)
+    a_in = _pad_cols(attn_vec, dp).contiguous()
+    grad_r = torch.empty((n_src, heads, dp), dtype=r.dtype, device=r.device)
+    if n_src > 0:
+        sched = _sched(row_ptr_T, light_nodes, heavy_nodes)
+        ws, ws_bytes = _scratch(_abi.OP_GATV2_BWD_SRC, sched, r_in, row_ptr_T.dtype, heads * dp)
+        args = _abi.Gatv2BwdSrcArgs(
+            exec=_abi.exec_of(r_in),
+            csr_t=_abi.csr_of(row_ptr_T, col_idx_T, l.shape[0]),
+            sched=sched.to_struct(_clamp_light(light_warps), _clamp_heavy(heavy_warps)),
             grad_out=_abi.mat_of(g_in),
             l=_abi.mat_of(l_in),
             r=_abi.mat_of(r_in),
@@ -598,16 +601,42 @@ def gatv2_backward(grad_h, l, r, row_ptr, col_idx, row_ptr_T, col_idx_T, attn_ve
             head_dim=dp,
             negative_slope=float(negative_slope),
             grad_r=_abi.mat_of(grad_r),
-            workspace=_abi.ptr(ws2),
-            workspace_bytes=ws2_bytes,
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
         )
-        _abi.call("tgnn_gatv2_backward_src", src_args)
-    else:
-        grad_r.zero_()
-    grad_a = grad_a32.to(attn_vec.dtype)
-    if dp != d:
-        grad_l, grad_r, grad_a = grad_l[..., :d].contiguous(), grad_r[..., :d].contiguous(), grad_a[:, :d].contiguous()
-    return [grad_l, grad_r, grad_a]
+        _abi.call("tgnn_gatv2_backward_src", args)
+    return _strip(grad_r, d)
+
+
+def gatv2_backward(grad_h, l, r, row_ptr, col_idx, row_ptr_T, col_idx_T, attn_vec, logsumexp, negative_slope,
+                   grad_A_reduce_row_chunk_size, fwd_light_nodes, fwd_heavy_nodes, bwd_light_nodes, bwd_heavy_nodes,
+                   light_warps_per_block=1, heavy_warps_per_block=8, is_directed=True, out=None):
+    """``[grad_l, grad_r, grad_attn]`` (``csrc/turbo_gnn.cpp:27-33``).
+
+    Two passes: destination side over the forward CSR (grad_l, grad_attn), source side over the
+    transposed CSR (grad_r).  ``is_directed=False`` means the caller aliased the transposed CSR to
+    the forward one; the same two passes run on it.  ``grad_A_reduce_row_chunk_size`` belonged to a
+    separate reduction kernel of the reference and is validated only.  ``out`` is the forward
+    result; without it the forward is recomputed to obtain ``G = <grad_h, out>``.
+    """
+    if grad_A_reduce_row_chunk_size not in (32, 64, 128, 256, 512, 1024, 2048):
+        raise RuntimeError("Wrong int value")
+    _check_attention_inputs(l, r, attn_vec, grad_h)
+    _check_index_family(row_ptr, col_idx, row_ptr_T, col_idx_T, fwd_light_nodes, fwd_heavy_nodes, bwd_light_nodes,
+                        bwd_heavy_nodes)
+    n_rows, heads, d = l.shape
+    if out is None:
+        out = gatv2_forward(l, r, row_ptr, col_idx, attn_vec, negative_slope, fwd_light_nodes, fwd_heavy_nodes)[0]
+    dp = _padded_head_dim(d)
+    grad_h = grad_h.reshape(n_rows, heads, d)
+    G = head_dot(_head_rows(grad_h, dp), _head_rows(out.reshape(n_rows, heads, d), dp))
+    lse = logsumexp.contiguous()
+    lw, hw = light_warps_per_block, heavy_warps_per_block
+    grad_l, grad_a32 = gatv2_backward_dst(grad_h, l, r, row_ptr, col_idx, attn_vec, lse, G, negative_slope,
+                                          fwd_light_nodes, fwd_heavy_nodes, lw, hw)
+    grad_r = gatv2_backward_src(grad_h, l, r, row_ptr_T, col_idx_T, attn_vec, lse, G, negative_slope,
+                                bwd_light_nodes, bwd_heavy_nodes, lw, hw)
+    return [grad_l, grad_r, _strip(grad_a32.to(attn_vec.dtype), d)]
 
 
 # ---------------------------------------------------------------------------------------
@@ -617,7 +646,10 @@ def gatv2_backward(grad_h, l, r, row_ptr, col_idx, row_ptr_T, col_idx_T, attn_ve
 
 def gt_forward_csr_mh(row_ptr, col_idx, Q, K, V, scale, light_nodes, heavy_nodes, light_warps_per_block=4,
                       heavy_warps_per_block=8):
-    """``(O [N,H,D], logsumexp [N,H])`` (``csrc/turbo_gnn.cpp:36-40``); score = <Q[src], K[dst]> * scale."""
+    """``(O [N,H,D], logsumexp [N,H])`` (``csrc/turbo_gnn.cpp:36-40``); score = <Q[src], K[dst]> * scale.
+
+    ``K`` has one row per CSR row (destinations), ``Q`` and ``V`` one row per CSR column (sources).
+    """
     _check_attention_inputs(Q, K, V)
     _check_index_family(row_ptr, col_idx, light_nodes, heavy_nodes)
     n_rows, heads, d = K.shape
@@ -645,9 +677,74 @@ def gt_forward_csr_mh(row_ptr, col_idx, Q, K, V, scale, light_nodes, heavy_nodes
             workspace_bytes=ws_bytes,
         )
         _abi.call("tgnn_gt_forward", args)
-    if dp != d:
-        out = out[..., :d].contiguous()
-    return out, lse
+    return _strip(out, d), lse
+
+
+def gt_backward_dst(row_ptr, col_idx, Q, K, V, dO, lse, delta, scale, light_nodes, heavy_nodes, light_warps=1,
+                    heavy_warps=8):
+    """Destination-side pass over the forward CSR: ``dK``.  K, dO, lse, delta: one row per CSR row."""
+    n_rows, heads, d = K.shape
+    dp = _padded_head_dim(d)
+    q_in, k_in, v_in, g_in = _head_rows(Q, dp), _head_rows(K, dp), _head_rows(V, dp), _head_rows(dO, dp)
+    dk = torch.empty((n_rows, heads, dp), dtype=K.dtype, device=K.device)
+    if n_rows > 0:
+        sched = _sched(row_ptr, light_nodes, heavy_nodes)
+        ws, ws_bytes = _scratch(_abi.OP_GT_BWD_DST, sched, k_in, row_ptr.dtype, heads * dp)
+        args = _abi.GtBwdDstArgs(
+            exec=_abi.exec_of(k_in),
+            csr=_abi.csr_of(row_ptr, col_idx, Q.shape[0]),
+            sched=sched.to_struct(_clamp_light(light_warps), _clamp_heavy(heavy_warps)),
+            q=_abi.mat_of(q_in),
+            k=_abi.mat_of(k_in),
+            v=_abi.mat_of(v_in),
+            d_out=_abi.mat_of(g_in),
+            lse=_abi.ptr(lse),
+            delta=_abi.ptr(delta),
+            heads=heads,
+            head_dim=dp,
+            scale=float(scale),
+            dk=_abi.mat_of(dk),
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
+        )
+        _abi.call("tgnn_gt_backward_dst", args)
+    return _strip(dk, d)
+
+
+def gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_nodes, heavy_nodes, light_warps=1,
+                    heavy_warps=8):
+    """Source-side pass over the transposed CSR: ``(dQ, dV)``.
+
+    Q, V: one row per row of the transposed CSR; K, dO, lse, delta: one row per column of it.
+    """
+    n_src, heads, d = Q.shape
+    dp = _padded_head_dim(d)
+    q_in, k_in, v_in, g_in = _head_rows(Q, dp), _head_rows(K, dp), _head_rows(V, dp), _head_rows(dO, dp)
+    dq = torch.empty((n_src, heads, dp), dtype=Q.dtype, device=Q.device)
+    dv = torch.empty((n_src, heads, dp), dtype=Q.dtype, device=Q.device)
+    if n_src > 0:
+        sched = _sched(row_ptr_T, light_nodes, heavy_nodes)
+        ws, ws_bytes = _scratch(_abi.OP_GT_BWD_SRC, sched, q_in, row_ptr_T.dtype, heads * dp)
+        args = _abi.GtBwdSrcArgs(
+            exec=_abi.exec_of(q_in),
+            csr_t=_abi.csr_of(row_ptr_T, col_idx_T, K.shape[0]),
+            sched=sched.to_struct(_clamp_light(light_warps), _clamp_heavy(heavy_warps)),
+            q=_abi.mat_of(q_in),
+            k=_abi.mat_of(k_in),
+            v=_abi.mat_of(v_in),
+            d_out=_abi.mat_of(g_in),
+            lse=_abi.ptr(lse),
+            delta=_abi.ptr(delta),
+            heads=heads,
+            head_dim=dp,
+            scale=float(scale),
+            dq=_abi.mat_of(dq),
+            dv=_abi.mat_of(dv),
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
+        )
+        _abi.call("tgnn_gt_backward_src", args)
+    return _strip(dq, d), _strip(dv, d)
 
 
 def gt_backward_csr_mh(row_ptr, col_idx, row_ptr_T, col_idx_T, Q, K, V, O, dO, logsumexp, scale, light_nodes,
@@ -662,66 +759,50 @@ def gt_backward_csr_mh(row_ptr, col_idx, row_ptr_T, col_idx_T, Q, K, V, O, dO, l
     _check_attention_inputs(Q, K, V, O, dO)
     _check_index_family(row_ptr, col_idx, row_ptr_T, col_idx_T, light_nodes, heavy_nodes)
     n_rows, heads, d = K.shape
-    n_src = Q.shape[0]
-    lw, hw = _clamp_light(light_warps_per_block), _clamp_heavy(heavy_warps_per_block)
     dp = _padded_head_dim(d)
-    q_in, k_in, v_in = _head_rows(Q, dp), _head_rows(K, dp), _head_rows(V, dp)
-    o_in = _head_rows(O.reshape(n_rows, heads, d), dp)
-    g_in = _head_rows(dO.reshape(n_rows, heads, d), dp)
+    dO = dO.reshape(n_rows, heads, d)
+    if fwd_light_nodes is None or fwd_heavy_nodes is None:
+        fwd_light_nodes, fwd_heavy_nodes = _bucket(row_ptr)
+    delta = head_dot(_head_rows(dO, dp), _head_rows(O.reshape(n_rows, heads, d), dp))
     lse = logsumexp.contiguous()
-    dq = torch.empty((n_src, heads, dp), dtype=Q.dtype, device=Q.device)
-    dv = torch.empty((n_src, heads, dp), dtype=Q.dtype, device=Q.device)
-    dk = torch.empty((n_rows, heads, dp), dtype=Q.dtype, device=Q.device)
+    lw, hw = light_warps_per_block, heavy_warps_per_block
+    dk = gt_backward_dst(row_ptr, col_idx, Q, K, V, dO, lse, delta, scale, fwd_light_nodes, fwd_heavy_nodes, lw, hw)
+    dq, dv = gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_nodes, heavy_nodes, lw, hw)
+    return dq, dk, dv
+
+
+# ---------------------------------------------------------------------------------------
+# weighted sum over an explicit CSR with caller-chosen row lists (used by the sharded ops)
+# ---------------------------------------------------------------------------------------
+
+
+def spmm_rows(indptr, indices, x, light_nodes, heavy_nodes, row_scale=None, col_scale=None, edge_weight=None,
+              light_warps=8, heavy_warps=8):
+    """``out[v] = row_scale[v] * sum_{e: u->v} edge_weight[e] * col_scale[u] * x[u]`` for every CSR row.
+
+    ``x`` has one row per CSR column; the result has one row per CSR row.  No caching, no
+    normalisation logic: the caller supplies tiers and scale vectors (fp32, optional).
+    """
+    _check_index_family(indptr, indices, light_nodes, heavy_nodes)
+    n_rows = indptr.numel() - 1
+    feat = x.shape[1]
+    cols = _round_up(max(feat, 1), _chunk_elems(x.dtype))
+    x_in = _as_rows(_pad_cols(x, cols))
+    out = torch.empty((n_rows, cols), dtype=x.dtype, device=x.device)
     if n_rows > 0:
-        if fwd_light_nodes is None or fwd_heavy_nodes is None:
-            fwd_light_nodes, fwd_heavy_nodes = _default_buckets(row_ptr)
-        delta = _head_dot(g_in, o_in, heads, dp)
-        ex = _abi.exec_of(q_in)
-        cols = heads * dp
-        f_sched = _sched(row_ptr, fwd_light_nodes, fwd_heavy_nodes)
-        ws, ws_bytes = _scratch(_abi.OP_GT_BWD_DST, f_sched, q_in, row_ptr.dtype, cols)
-        dst_args = _abi.GtBwdDstArgs(
-            exec=ex,
-            csr=_abi.csr_of(row_ptr, col_idx, n_src),
-            sched=f_sched.to_struct(lw, hw),
-            q=_abi.mat_of(q_in),
-            k=_abi.mat_of(k_in),
-            v=_abi.mat_of(v_in),
-            d_out=_abi.mat_of(g_in),
-            lse=_abi.ptr(lse),
-            delta=_abi.ptr(delta),
-            heads=heads,
-            head_dim=dp,
-            scale=float(scale),
-            dk=_abi.mat_of(dk),
+        sched = _sched(indptr, light_nodes, heavy_nodes)
+        ws, ws_bytes = _scratch(_abi.OP_WEIGHTED_SUM, sched, x_in, indptr.dtype, cols)
+        args = _abi.SpmmArgs(
+            exec=_abi.exec_of(x_in),
+            csr=_abi.csr_of(indptr, indices, x.shape[0]),
+            sched=sched.to_struct(light_warps, heavy_warps),
+            x=_abi.mat_of(x_in),
+            out=_abi.mat_of(out),
+            row_scale=_abi.ptr(row_scale),
+            col_scale=_abi.ptr(col_scale),
+            edge_weight=_abi.ptr(edge_weight),
             workspace=_abi.ptr(ws),
             workspace_bytes=ws_bytes,
         )
-        _abi.call("tgnn_gt_backward_dst", dst_args)
-        b_sched = _sched(row_ptr_T, light_nodes, heavy_nodes)
-        ws2, ws2_bytes = _scratch(_abi.OP_GT_BWD_SRC, b_sched, q_in, row_ptr.dtype, cols)
-        src_args = _abi.GtBwdSrcArgs(
-            exec=ex,
-            csr_t=_abi.csr_of(row_ptr_T, col_idx_T, n_rows),
-            sched=b_sched.to_struct(lw, hw),
-            q=_abi.mat_of(q_in),
-            k=_abi.mat_of(k_in),
-            v=_abi.mat_of(v_in),
-            d_out=_abi.mat_of(g_in),
-            lse=_abi.ptr(lse),
-            delta=_abi.ptr(delta),
-            heads=heads,
-            head_dim=dp,
-            scale=float(scale),
-            dq=_abi.mat_of(dq),
-            dv=_abi.mat_of(dv),
-            workspace=_abi.ptr(ws2),
-            workspace_bytes=ws2_bytes,
-        )
-        _abi.call("tgnn_gt_backward_src", src_args)
-    else:
-        dq.zero_()
-        dv.zero_()
-    if dp != d:
-        dq, dk, dv = dq[..., :d].contiguous(), dk[..., :d].contiguous(), dv[..., :d].contiguous()
-    return dq, dk, dv
+        _abi.call("tgnn_spmm", args)
+    return out if cols == feat else out[:, :feat].contiguous()

@@ -331,9 +331,50 @@ def last_error() -> str:
     return buf.value.decode(errors="replace")
 
 
+class CallTrace:
+    """Optional per-entry-point instrumentation, off by default.
+
+    While enabled, every library call is bracketed by CUDA events on the stream it runs on and
+    the number of kernels it launches is added up; ``bench.py`` reads both after its timed region.
+    """
+
+    def __init__(self):
+        self.enabled = False
+        self.events: dict[str, list] = {}
+        self.kernel_launches = 0
+
+    def reset(self, enabled: bool) -> None:
+        self.enabled = enabled
+        self.events = {}
+        self.kernel_launches = 0
+
+    def mean_ms(self) -> dict[str, float]:
+        """Mean device time per call of each entry point (call after a synchronize)."""
+        return {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in self.events.items() if v}
+
+
+trace = CallTrace()
+
+
+def _kernels_of(args: C.Structure) -> int:
+    sched = getattr(args, "sched", None)
+    if sched is None:
+        return 1
+    return int(sched.num_light > 0) + int(sched.num_heavy > 0) + 2 * int(sched.num_hub > 0)
+
+
 def call(name: str, args: C.Structure) -> None:
     """Invoke an entry point; a non-zero status becomes RuntimeError."""
-    status = getattr(load_library(), name)(C.byref(args))
+    fn = getattr(load_library(), name)
+    if trace.enabled:
+        begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        status = fn(C.byref(args))
+        finish.record()
+        trace.events.setdefault(name, []).append((begin, finish))
+        trace.kernel_launches += _kernels_of(args)
+    else:
+        status = fn(C.byref(args))
     if status != OK:
         raise RuntimeError(f"{name} failed with status {status}: {last_error()}")
 

@@ -1,0 +1,259 @@
+"""Multi-GPU execution: edge-balanced node partition + all-gather of the gathered-from features.
+
+The reference is single-GPU.  Here one process drives one GPU (``torch.distributed``, NCCL over
+NVLink).  Nodes are cut into ``world`` contiguous ranges holding about the same number of edges;
+rank p owns range p in both roles:
+
+* as DESTINATIONS: its slice of the forward CSR (rows = owned nodes) -- forward pass and the
+  destination-side backward pass write only owned rows;
+* as SOURCES: its slice of the transposed CSR (rows = owned nodes) -- the source-side backward
+  pass writes only owned rows, so no gradient ever has to be reduced across ranks.
+
+What a pass gathers FROM (source features in forward, destination-side tensors in the
+source-side backward) is all-gathered into a local buffer first, one collective per pass;
+kernels then run unchanged on local memory.  Ranges have unequal lengths, so the gathered
+buffer is laid out ``[world, max_rows, F]`` (each rank's rows padded to the longest range) and
+the column ids of the shards are remapped once to that layout; this keeps the collective a
+single equal-sized ``all_gather_into_tensor``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import _C
+from .graph import AdjacencyForwardBackwardWithNodeBuckets, _row_degrees
+
+
+def edge_balanced_bounds(fwd_indptr: torch.Tensor, bwd_indptr: torch.Tensor, world: int) -> list[int]:
+    """``world + 1`` node boundaries; every range holds ~1/world of (in-edges + out-edges)."""
+    n = fwd_indptr.numel() - 1
+    load = (_row_degrees(fwd_indptr) + _row_degrees(bwd_indptr)).long()
+    prefix = torch.cumsum(load, 0)
+    total = int(prefix[-1].item()) if n > 0 else 0
+    targets = torch.tensor([total * p // world for p in range(1, world)], dtype=prefix.dtype, device=prefix.device)
+    cuts = torch.searchsorted(prefix, targets, right=False).tolist() if world > 1 else []
+    bounds = [0] + [min(max(int(c) + 1, 0), n) for c in cuts] + [n]
+    for i in range(1, len(bounds)):  # keep the boundaries monotone
+        bounds[i] = max(bounds[i], bounds[i - 1])
+    return bounds
+
+
+def remap_to_padded(ids: torch.Tensor, bounds: list[int], max_rows: int) -> torch.Tensor:
+    """Global node id -> row in the ``[world, max_rows]`` gathered layout."""
+    b = torch.tensor(bounds, dtype=torch.long, device=ids.device)
+    owner = torch.bucketize(ids.long(), b[1:], right=True)
+    return (owner * max_rows + ids.long() - b[owner]).to(ids.dtype)
+
+
+@dataclass
+class GraphShard:
+    """What one rank holds of a partitioned graph."""
+
+    rank: int
+    world: int
+    bounds: list
+    max_rows: int
+    graph: AdjacencyForwardBackwardWithNodeBuckets  # rows = owned nodes, column ids in the padded layout
+    num_global_nodes: int
+
+    @property
+    def row_begin(self) -> int:
+        return self.bounds[self.rank]
+
+    @property
+    def num_local(self) -> int:
+        return self.bounds[self.rank + 1] - self.bounds[self.rank]
+
+    @property
+    def num_local_edges(self) -> int:
+        return self.graph.forward_indices.numel()
+
+    def local_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """Slice the owned rows out of a global per-node tensor."""
+        return t[self.bounds[self.rank]: self.bounds[self.rank + 1]]
+
+
+def _slice_csr(indptr, indices, r0, r1, bounds, max_rows):
+    sp = AdjacencyForwardBackwardWithNodeBuckets._to_signed_view(indptr)
+    e0, e1 = int(sp[r0].item()), int(sp[r1].item())
+    local_ptr = (sp[r0: r1 + 1] - sp[r0]).to(indptr.dtype).contiguous()
+    cols = AdjacencyForwardBackwardWithNodeBuckets._to_signed_view(indices)[e0:e1]
+    return local_ptr, remap_to_padded(cols, bounds, max_rows).contiguous()
+
+
+def shard_graph(graph: AdjacencyForwardBackwardWithNodeBuckets, rank: int, world: int, quantile: float = 0.99,
+                bounds: list | None = None) -> GraphShard:
+    """Cut rank ``rank``'s shard out of a full graph (every rank calls this on the same graph)."""
+    n = graph.forward_indptr.numel() - 1
+    bounds = bounds or edge_balanced_bounds(graph.forward_indptr, graph.backward_indptr, world)
+    max_rows = max(bounds[p + 1] - bounds[p] for p in range(world))
+    max_rows = max((max_rows + 7) // 8 * 8, 8)
+    r0, r1 = bounds[rank], bounds[rank + 1]
+    f_ptr, f_idx = _slice_csr(graph.forward_indptr, graph.forward_indices, r0, r1, bounds, max_rows)
+    b_ptr, b_idx = _slice_csr(graph.backward_indptr, graph.backward_indices, r0, r1, bounds, max_rows)
+    local = AdjacencyForwardBackwardWithNodeBuckets.from_csr(f_ptr, f_idx, b_ptr, b_idx, quantile=quantile,
+                                                            is_directed=True)
+    return GraphShard(rank, world, bounds, max_rows, local, n)
+
+
+def gather_rows(local: torch.Tensor, shard: GraphShard, group=None, async_op: bool = False):
+    """All-gather a row-sharded tensor into the padded ``[world * max_rows, ...]`` layout.
+
+    Returns the gathered tensor (and the work handle when ``async_op``).  With ``world == 1`` the
+    result is the zero-padded input and no collective runs.
+    """
+    tail = tuple(local.shape[1:])
+    staged = torch.zeros((shard.max_rows,) + tail, dtype=local.dtype, device=local.device)
+    staged[: local.shape[0]].copy_(local)
+    if shard.world == 1:
+        return (staged, None) if async_op else staged
+    full = torch.empty((shard.world * shard.max_rows,) + tail, dtype=local.dtype, device=local.device)
+    work = dist.all_gather_into_tensor(full, staged, group=group, async_op=async_op)
+    return (full, work) if async_op else full
+
+
+class _ShardedGraphTransformer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, shard, Q, K, V, scale, launch, group):
+        g = shard.graph
+        n, heads, d = Q.shape
+        qv = gather_rows(torch.cat([Q, V], dim=1), shard, group)  # [W*max, 2H, D]
+        q_full, v_full = qv[:, :heads], qv[:, heads:]
+        out, lse = _C.gt_forward_csr_mh(g.forward_indptr, g.forward_indices, q_full, K, v_full, scale,
+                                        g.forward_light_nodes, g.forward_heavy_nodes, launch[0], launch[1])
+        ctx.shard, ctx.scale, ctx.launch, ctx.group = shard, scale, launch, group
+        ctx.save_for_backward(Q, K, V, qv, out, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        Q, K, V, qv, out, lse = ctx.saved_tensors
+        shard, g = ctx.shard, ctx.shard.graph
+        n, heads, d = Q.shape
+        grad_out = grad_out.contiguous()
+        delta = _C.head_dot(_C._head_rows(grad_out, _C._padded_head_dim(d)), _C._head_rows(out, _C._padded_head_dim(d)))
+        # Destination-side tensors travel while the destination-side pass (local data only) runs.
+        kd, work_a = gather_rows(torch.cat([K, grad_out], dim=1), shard, ctx.group, async_op=True)
+        stats, work_b = gather_rows(torch.cat([lse, delta], dim=1), shard, ctx.group, async_op=True)
+        q_full, v_full = qv[:, :heads], qv[:, heads:]
+        dk = _C.gt_backward_dst(g.forward_indptr, g.forward_indices, q_full, K, v_full, grad_out, lse, delta,
+                                ctx.scale, g.forward_light_nodes, g.forward_heavy_nodes, ctx.launch[2], ctx.launch[3])
+        for w in (work_a, work_b):
+            if w is not None:
+                w.wait()
+        k_full, do_full = kd[:, :heads], kd[:, heads:]
+        lse_full, delta_full = stats[:, :heads].contiguous(), stats[:, heads:].contiguous()
+        dq, dv = _C.gt_backward_src(g.backward_indptr, g.backward_indices, Q, k_full, V, do_full, lse_full,
+                                    delta_full, ctx.scale, g.backward_light_nodes, g.backward_heavy_nodes,
+                                    ctx.launch[2], ctx.launch[3])
+        return None, dq, dk, dv, None, None, None
+
+
+def sharded_graph_transformer_aggr(shard: GraphShard, Q, K, V, scale=None, forward_light_warps=4,
+                                   forward_heavy_warps=8, backward_light_warps=1, backward_heavy_warps=8,
+                                   group=None):
+    """``graph_transformer_aggr`` on a row shard: Q, K, V and the result hold the owned rows only."""
+    scale = scale or 1 / (Q.shape[-1] ** 0.5)
+    launch = (forward_light_warps, forward_heavy_warps, backward_light_warps, backward_heavy_warps)
+    return _ShardedGraphTransformer.apply(shard, Q, K, V, scale, launch, group)
+
+
+class _ShardedGatv2(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, shard, x_left, x_right, attn, slope, launch, group):
+        g = shard.graph
+        r_full = gather_rows(x_right, shard, group)
+        out, lse = _C.gatv2_forward(x_left, r_full, g.forward_indptr, g.forward_indices, attn, slope,
+                                    g.forward_light_nodes, g.forward_heavy_nodes, launch[0], launch[1])
+        ctx.shard, ctx.slope, ctx.launch, ctx.group = shard, slope, launch, group
+        ctx.save_for_backward(x_left, x_right, attn, r_full, out, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x_left, x_right, attn, r_full, out, lse = ctx.saved_tensors
+        shard, g = ctx.shard, ctx.shard.graph
+        n, heads, d = x_left.shape
+        dp = _C._padded_head_dim(d)
+        grad_out = grad_out.contiguous()
+        G = _C.head_dot(_C._head_rows(grad_out, dp), _C._head_rows(out, dp))
+        lg, work_a = gather_rows(torch.cat([x_left, grad_out], dim=1), shard, ctx.group, async_op=True)
+        stats, work_b = gather_rows(torch.cat([lse, G], dim=1), shard, ctx.group, async_op=True)
+        grad_l, grad_a32 = _C.gatv2_backward_dst(grad_out, x_left, r_full, g.forward_indptr, g.forward_indices, attn,
+                                                 lse, G, ctx.slope, g.forward_light_nodes, g.forward_heavy_nodes,
+                                                 ctx.launch[2], ctx.launch[3])
+        for w in (work_a, work_b):
+            if w is not None:
+                w.wait()
+        l_full, gh_full = lg[:, :heads], lg[:, heads:]
+        lse_full, G_full = stats[:, :heads].contiguous(), stats[:, heads:].contiguous()
+        grad_r = _C.gatv2_backward_src(gh_full, l_full, x_right, g.backward_indptr, g.backward_indices, attn,
+                                       lse_full, G_full, ctx.slope, g.backward_light_nodes, g.backward_heavy_nodes,
+                                       ctx.launch[2], ctx.launch[3])
+        if shard.world > 1:
+            dist.all_reduce(grad_a32, group=ctx.group)  # the attention vector is replicated
+        grad_a = grad_a32[:, :d].to(attn.dtype)
+        return None, grad_l, grad_r, grad_a, None, None, None
+
+
+def sharded_gatv2_aggr(shard: GraphShard, x, x_neighbors, attention_weights, negative_slope=0.2,
+                       forward_light_warps=1, forward_heavy_warps=8, backward_light_warps=1, backward_heavy_warps=8,
+                       group=None):
+    """``gatv2_aggr`` on a row shard; the attention-vector gradient is all-reduced."""
+    launch = (forward_light_warps, forward_heavy_warps, backward_light_warps, backward_heavy_warps)
+    return _ShardedGatv2.apply(shard, x, x_neighbors, attention_weights, negative_slope, launch, group)
+
+
+class _ShardedSpmm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, shard, x, scales, group):
+        g = shard.graph
+        row_scale, col_scale_full, t_row_scale, t_col_scale_full = scales
+        x_full = gather_rows(x, shard, group)
+        ctx.shard, ctx.group, ctx.scales = shard, group, scales
+        return _C.spmm_rows(g.forward_indptr, g.forward_indices, x_full, g.forward_light_nodes,
+                            g.forward_heavy_nodes, row_scale, col_scale_full)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        shard, g = ctx.shard, ctx.shard.graph
+        _, _, t_row_scale, t_col_scale_full = ctx.scales
+        g_full = gather_rows(grad_out.contiguous(), shard, ctx.group)
+        grad_x = _C.spmm_rows(g.backward_indptr, g.backward_indices, g_full, g.backward_light_nodes,
+                              g.backward_heavy_nodes, t_row_scale, t_col_scale_full)
+        return None, grad_x, None, None
+
+
+def sharded_norm_scales(shard: GraphShard, norm: str, group=None):
+    """Scale vectors of a normalised SpMM for both directions of a shard.
+
+    Returns ``(row_scale, col_scale_full, t_row_scale, t_col_scale_full)``: forward rows are
+    destinations (in-degree), transposed rows are sources (out-degree); the ``*_full`` vectors are
+    in the padded gathered layout.  ``None`` entries mean "all ones".
+    """
+    if norm == "none":
+        return (None, None, None, None)
+    g = shard.graph
+    in_deg = _row_degrees(g.forward_indptr).float().clamp(min=1)
+    out_deg = _row_degrees(g.backward_indptr).float().clamp(min=1)
+    if norm == "right":
+        dst_s, src_s = 1.0 / in_deg, None
+    elif norm == "left":
+        dst_s, src_s = None, 1.0 / out_deg
+    elif norm == "both":
+        dst_s, src_s = in_deg.rsqrt(), out_deg.rsqrt()
+    else:
+        raise RuntimeError(f"unknown norm '{norm}'")
+    src_full = None if src_s is None else gather_rows(src_s.unsqueeze(1), shard, group).squeeze(1).contiguous()
+    dst_full = None if dst_s is None else gather_rows(dst_s.unsqueeze(1), shard, group).squeeze(1).contiguous()
+    return (dst_s, src_full, src_s, dst_full)
+
+
+def sharded_spmm_aggr(shard: GraphShard, x, norm: str = "none", scales=None, group=None):
+    """Normalised SpMM on a row shard (``x`` and the result hold the owned rows)."""
+    scales = scales if scales is not None else sharded_norm_scales(shard, norm, group)
+    return _ShardedSpmm.apply(shard, x, scales, group)

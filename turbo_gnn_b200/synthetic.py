@@ -117,7 +117,7 @@ def make_workload(cfg: int, device="cuda", shrink: float = 1.0, index_dtype=None
                         {"reduce": ["min", "max", "sum", "mean"]})
     if cfg == 1:
         n = _shrunk(169_343, shrink)
-        w = power_law_weights(n, 2.0, 1.0, float(max(n // 10, 8)), 7.0, gen)
+        w = power_law_weights(n, 2.0, 1.0, float(max(n // 170, 8)), 6.887, gen)
         e = chung_lu_edges(n, _shrunk(1_166_243, shrink), w, w, gen)
         e = dedup_edges(add_self_loops(symmetrise(e), n), n)
         g = graph_from_edges(e, n, index_dtype or torch.int32, quantile)
@@ -126,10 +126,10 @@ def make_workload(cfg: int, device="cuda", shrink: float = 1.0, index_dtype=None
         return Workload("cfg1_gatv2", "gatv2", n, e, g, t, {"negative_slope": 0.2})
     if cfg == 2:
         n = _shrunk(232_965, shrink)
-        mean_deg = 492.0 * min(1.0, max(shrink, 0.05) * 4) if shrink < 0.25 else 492.0
-        hi = min(21_000.0, n / 2)
-        w = power_law_weights(n, 2.2, 60.0, hi * 1.25, mean_deg, gen)
-        e = chung_lu_edges(n, int(n * mean_deg * 1.035), w, w, gen)
+        mean_deg = min(492.0, n / 8)
+        hi = min(19_000.0, n / 2)
+        w = power_law_weights(n, 2.2, min(95.0, hi / 8), hi, mean_deg, gen)
+        e = chung_lu_edges(n, int(n * mean_deg * 1.04), w, w, gen)
         e = dedup_edges(e, n)
         g = graph_from_edges(e, n, index_dtype or torch.int32, quantile)
         t = {"Q": randn(n, 4, 64), "K": randn(n, 4, 64), "V": randn(n, 4, 64), "grad": randn(n, 4, 64)}
