@@ -1,0 +1,53 @@
+"""The three-tier schedule: every edge of every row is covered exactly once."""
+
+import pytest
+import torch
+
+from helpers import make_graph, random_edges
+from turbo_gnn_b200 import _schedule
+
+
+@pytest.mark.parametrize("chunk,hub_min", [(32, 64), (64, 100), (2048, 4096)])
+def test_tiers_partition_rows_and_chunks_cover_hub_rows(chunk, hub_min):
+    n = 400
+    ei = random_edges(n, 4000, 3, hubs=3, hub_degree=350)
+    g = make_graph(ei, n, torch.int32, quantile=0.9, device="cpu")
+    s = _schedule.split_tiers(g.forward_indptr, g.forward_light_nodes, g.forward_heavy_nodes, chunk, hub_min)
+    rows = torch.cat([s.light, s.heavy, s.hub]).long()
+    assert sorted(rows.tolist()) == list(range(n))
+    ptr = g.forward_indptr.long()
+    deg = ptr[1:] - ptr[:-1]
+    assert bool((deg[s.hub.long()] >= hub_min).all()) and bool((deg[s.heavy.long()] < hub_min).all())
+    assert s.hub_part_ptr[0].item() == 0 and s.hub_part_ptr[-1].item() == s.num_chunks == s.chunk_hub.numel()
+    covered = torch.zeros(int(ptr[-1]), dtype=torch.int32)
+    for c in range(s.num_chunks):
+        k = int(s.chunk_hub[c])
+        row = int(s.hub[k])
+        e0 = int(ptr[row]) + (c - int(s.hub_part_ptr[k])) * chunk
+        e1 = min(e0 + chunk, int(ptr[row + 1]))
+        assert e0 < e1
+        covered[e0:e1] += 1
+    for row in s.hub.tolist():
+        assert bool((covered[int(ptr[row]): int(ptr[row + 1])] == 1).all())
+    # light rows are ordered longest first
+    ld = deg[s.light.long()]
+    assert bool((ld[:-1] >= ld[1:]).all())
+
+
+def test_cache_hits_on_same_tensors_and_misses_on_new_ones():
+    n = 100
+    g = make_graph(random_edges(n, 800, 1), n, torch.int64, quantile=0.9, device="cpu")
+    a = _schedule.get_schedule(g.forward_indptr, g.forward_light_nodes, g.forward_heavy_nodes)
+    b = _schedule.get_schedule(g.forward_indptr, g.forward_light_nodes, g.forward_heavy_nodes)
+    assert a is b
+    c = _schedule.get_schedule(g.forward_indptr, g.forward_light_nodes, g.forward_heavy_nodes, chunk_edges=64)
+    assert c is not a
+    r = g.repartition(forward_huge_degree_threshold_quantile=0.5)
+    d = _schedule.get_schedule(r.forward_indptr, r.forward_light_nodes, r.forward_heavy_nodes)
+    assert d is not a and d.light.numel() != a.light.numel()
+
+
+def test_bad_chunk_size_raises_runtime_error():
+    g = make_graph(random_edges(50, 300, 2), 50, torch.int32, device="cpu")
+    with pytest.raises(RuntimeError):
+        _schedule.split_tiers(g.forward_indptr, g.forward_light_nodes, g.forward_heavy_nodes, chunk_edges=48)
