@@ -200,7 +200,7 @@ class Job:
             return (out,) + torch.autograd.grad(out, x, self.grad)
         outs = []
         for red in ("min", "max", "sum", "mean"):  # cfg0: forward only, four reductions
-            outs.append(tg.reduction_aggr(g, x[0], reduce=red))
+            outs.append(tg.reduction_aggr(g, x[0], warps_per_block=4, reduce=red))
         return tuple(outs)
 
     # ---- byte model (algorithmic bytes of one call of each library entry point, this rank) ----
@@ -346,7 +346,8 @@ def run_cpu(args, steps, warmup):
 def config_of(args, job=None):
     cfg = {"workload": args.workload, "shrink": args.shrink, "l2": "inputs larger than L2 (no flush)"}
     if job is not None:
-        cfg.update({"nodes": job.num_nodes, "edges": job.total_edges, "index_dtype": "int32",
+        cfg.update({"nodes": job.num_nodes, "edges": job.total_edges,
+                    "index_dtype": str(job.graph.index_dtype).replace("torch.", ""),
                     "quantile": args.quantile, "op": job.op,
                     "parallelism": f"row-partition x{job.world}" if job.world > 1 else "single"})
     return cfg

@@ -1,0 +1,117 @@
+"""Row-partitioned execution, host logic only: two gloo ranks on CPU.
+
+Each rank cuts its shard, all-gathers the source features into the padded layout and evaluates
+the ORACLE on its shard's edges; the concatenation of the per-rank results must equal the oracle
+on the whole graph.  This exercises the partition, the column remap and the collective without a GPU.
+"""
+
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import make_graph, random_edges
+from oracle import scatter_oracle as O
+from turbo_gnn_b200 import dist as tdist
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _shard_edges(shard):
+    """COO of a shard's forward CSR: sources in the padded layout, destinations local."""
+    g = shard.graph
+    ptr = g.forward_indptr.long()
+    dst = torch.repeat_interleave(torch.arange(shard.num_local), ptr[1:] - ptr[:-1])
+    return torch.stack([g.forward_indices.long(), dst])
+
+
+def _transposed_shard_edges(shard):
+    g = shard.graph
+    ptr = g.backward_indptr.long()
+    src_local = torch.repeat_interleave(torch.arange(shard.num_local), ptr[1:] - ptr[:-1])
+    return g.backward_indices.long(), src_local  # (padded destination id, local source id)
+
+
+def _worker(rank, world, port, n, seed, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ei = random_edges(n, 6 * n, seed, hubs=2, hub_degree=n // 3)
+        graph = make_graph(ei, n, torch.int64, quantile=0.9, device="cpu")
+        shard = tdist.shard_graph(graph, rank, world, quantile=0.9)
+        g = torch.Generator().manual_seed(seed + 1)
+        q, k, v = (torch.randn(n, 2, 4, generator=g, dtype=torch.float64) for _ in range(3))
+        x = torch.randn(n, 6, generator=g, dtype=torch.float64)
+
+        full_qv = tdist.gather_rows(torch.cat([shard.local_rows(q), shard.local_rows(v)], 1), shard)
+        q_full, v_full = full_qv[:, :2], full_qv[:, 2:]
+        sei = _shard_edges(shard)
+        # destination-side tensors are indexed by local row: pad K to the source-table length
+        rows_pad = shard.world * shard.max_rows
+        k_tab = torch.zeros(rows_pad, 2, 4, dtype=torch.float64)
+        k_tab[: shard.num_local] = shard.local_rows(k)
+        out_local = O.gt_aggregate(q_full, k_tab, v_full, sei, rows_pad, 0.5)[: shard.num_local]
+
+        x_full = tdist.gather_rows(shard.local_rows(x), shard)
+        red = {r: O.segment_reduce(x_full, sei, rows_pad, r)[: shard.num_local] for r in ("min", "sum", "mean")}
+
+        # transposed shard: out-degree of owned sources equals the global out-degree
+        dst_pad, src_local = _transposed_shard_edges(shard)
+        out_deg = torch.bincount(src_local, minlength=shard.num_local)
+        torch.save({"bounds": shard.bounds, "gt": out_local, "red": red, "out_deg": out_deg,
+                    "max_rows": shard.max_rows, "dst_pad_max": int(dst_pad.max()) if dst_pad.numel() else -1},
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_shards_reproduce_the_global_result(tmp_path):
+    n, seed, world = 120, 9, 2
+    mp.spawn(_worker, args=(world, _free_port(), n, seed, str(tmp_path)), nprocs=world, join=True)
+    parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(world)]
+    assert parts[0]["bounds"] == parts[1]["bounds"]
+    bounds = parts[0]["bounds"]
+    assert bounds[0] == 0 and bounds[-1] == n and bounds[1] > 0
+
+    ei = random_edges(n, 6 * n, seed, hubs=2, hub_degree=n // 3)
+    g = torch.Generator().manual_seed(seed + 1)
+    q, k, v = (torch.randn(n, 2, 4, generator=g, dtype=torch.float64) for _ in range(3))
+    x = torch.randn(n, 6, generator=g, dtype=torch.float64)
+    want = O.gt_aggregate(q, k, v, ei, n, 0.5)
+    got = torch.cat([p["gt"] for p in parts])
+    assert torch.allclose(got, want, atol=1e-12)
+    for r in ("min", "sum", "mean"):
+        got = torch.cat([p["red"][r] for p in parts])
+        assert torch.allclose(got, O.segment_reduce(x, ei, n, r), atol=1e-12), r
+    out_deg = torch.cat([p["out_deg"] for p in parts])
+    assert torch.equal(out_deg, torch.bincount(ei[0], minlength=n))
+    assert all(p["dst_pad_max"] < world * p["max_rows"] for p in parts)
+
+
+def test_edge_balanced_bounds_balance_edges():
+    n = 400
+    ei = random_edges(n, 5000, 3, hubs=4, hub_degree=300)
+    graph = make_graph(ei, n, torch.int32, device="cpu")
+    for world in (1, 2, 4, 8):
+        b = tdist.edge_balanced_bounds(graph.forward_indptr, graph.backward_indptr, world)
+        assert len(b) == world + 1 and b[0] == 0 and b[-1] == n and b == sorted(b)
+        load = (graph.forward_indptr[1:] - graph.forward_indptr[:-1]).long() + (
+            graph.backward_indptr[1:] - graph.backward_indptr[:-1]).long()
+        per = [int(load[b[p]: b[p + 1]].sum()) for p in range(world)]
+        assert sum(per) == int(load.sum())
+        assert max(per) <= int(load.sum()) / world + int(load.max())
+
+
+def test_remap_to_padded_layout():
+    bounds = [0, 3, 4, 9]
+    ids = torch.arange(9)
+    got = tdist.remap_to_padded(ids, bounds, 8)
+    assert got.tolist() == [0, 1, 2, 8, 16, 17, 18, 19, 20]
+    assert tdist.remap_to_padded(ids.int(), bounds, 8).dtype == torch.int32

@@ -1,0 +1,97 @@
+"""Normalised g-SpMM (the cuSPARSE replacement) on the GPU against the CPU oracle."""
+
+import pytest
+import torch
+
+import turbo_gnn_b200 as tg
+from helpers import make_graph, random_edges, rel_err
+from oracle import scatter_oracle as O
+from turbo_gnn_b200 import _C
+
+pytestmark = pytest.mark.gpu
+
+
+def _graph(n=1500, seed=1):
+    ei = random_edges(n, 10 * n, seed, hubs=3, hub_degree=n // 2)
+    return ei, make_graph(ei, n, torch.int32, quantile=0.9)
+
+
+@pytest.mark.parametrize("norm", ["none", "right", "left", "both"])
+@pytest.mark.parametrize("dt,feat,tol", [(torch.float32, 64, 1e-5), (torch.float32, 200, 1e-5),
+                                         (torch.bfloat16, 256, 2e-2), (torch.float16, 96, 2e-2)])
+def test_forward_and_backward(norm, dt, feat, tol):
+    n = 1500
+    ei, g = _graph()
+    x = torch.randn(n, feat, generator=torch.Generator().manual_seed(3)).to(dt)
+    up = torch.randn(n, feat, generator=torch.Generator().manual_seed(4)).to(dt)
+    xr = x.double().requires_grad_()
+    want = O.spmm(xr, ei, n, norm)
+    want.backward(up.double())
+    xc = x.cuda().requires_grad_()
+    _C.clear_graph_cache()
+    with _C.hub_tier(chunk_edges=128, hub_min_degree=400):
+        got = tg.spmm_aggr(xc, g.forward_indptr, g.forward_indices, norm, -1, 256)
+        got.backward(up.cuda())
+    assert got.dtype == dt and got.shape == (n, feat)
+    assert rel_err(got.float(), want) <= tol
+    assert rel_err(xc.grad.float(), xr.grad) <= tol
+
+
+def test_edge_weights_and_transpose_flag():
+    n = 700
+    ei, g = _graph(n=n, seed=5)
+    x = torch.randn(n, 32, generator=torch.Generator().manual_seed(6))
+    # weights are given in the edge order of the CSR that is passed in
+    w_csr = torch.rand(g.forward_indices.numel(), generator=torch.Generator().manual_seed(7)) + 0.5
+    ptr = g.forward_indptr.long().cpu()
+    dst = torch.repeat_interleave(torch.arange(n), ptr[1:] - ptr[:-1])
+    coo = torch.stack([g.forward_indices.long().cpu(), dst])
+    want = O.spmm(x.double(), coo, n, "both", edge_weight=w_csr.double())
+    got = tg.csr_SPMM_normalized(g.forward_indptr, g.forward_indices, x.cuda(), w_csr.cuda(), norm="both")
+    assert rel_err(got, want) <= 1e-5
+    # A^T with the same weights
+    want_t = O.scatter_add_rows(
+        x.double()[coo[1]] * (O.spmm_edge_weights(coo, n, "both", torch.float64) * w_csr.double()).unsqueeze(1),
+        coo[0], n)
+    got_t = tg.csr_SPMM_normalized(g.forward_indptr, g.forward_indices, x.cuda(), w_csr.cuda(), norm="both",
+                                   do_transpose_a=True)
+    assert rel_err(got_t, want_t) <= 1e-5
+
+
+def test_transpose_csr_is_exact():
+    n = 900
+    ei, g = _graph(n=n, seed=8)
+    t_ptr, t_idx, perm = _C.transpose_csr(g.forward_indptr, g.forward_indices, n)
+    assert torch.equal(t_ptr, g.backward_indptr) and torch.equal(t_idx, g.backward_indices)
+    assert perm.numel() == g.forward_indices.numel() and torch.equal(perm.sort().values,
+                                                                     torch.arange(perm.numel(), device=perm.device))
+
+
+def test_compute_degrees_and_compat_entry_points():
+    n = 400
+    ei, g = _graph(n=n, seed=9)
+    ind = torch.empty(n, dtype=torch.int32, device="cuda")
+    outd = torch.empty(n, dtype=torch.int32, device="cuda")
+    _C.compute_degrees(g.forward_indptr, g.forward_indices, ind, outd)
+    assert torch.equal(ind.cpu().long(), torch.bincount(ei[1], minlength=n))
+    assert torch.equal(outd.cpu().long(), torch.bincount(ei[0], minlength=n))
+    x = torch.randn(n, 16).cuda()
+    assert _C.find_best_algorithm(g.forward_indptr, g.forward_indices, x) == 0
+    a = _C.csr_SPMM(g.forward_indptr, g.forward_indices, x)
+    assert rel_err(a, O.spmm(x.cpu().double(), ei, n, "none")) <= 1e-5
+    _C.clear_graph_cache()
+
+
+def test_sum_and_mean_reductions_share_the_kernel():
+    n = 600
+    ei, g = _graph(n=n, seed=10)
+    x = torch.randn(n, 64, generator=torch.Generator().manual_seed(11)).cuda()
+    a = tg.reduction_aggr(g, x, warps_per_block=2, reduce="mean")
+    b = tg.spmm_aggr(x, g.forward_indptr, g.forward_indices, "right", -1, 256)
+    assert rel_err(a, b.cpu()) <= 1e-6
+
+
+def test_bad_norm_raises():
+    ei, g = _graph(n=100, seed=12)
+    with pytest.raises(RuntimeError):
+        tg.spmm_aggr(torch.randn(100, 8).cuda(), g.forward_indptr, g.forward_indices, "sideways", -1, 256)
