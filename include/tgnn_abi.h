@@ -217,6 +217,34 @@ typedef struct tgnn_spmm_args {
 } tgnn_spmm_args;
 int32_t tgnn_spmm(const tgnn_spmm_args *a);
 
+/* Same computation as tgnn_spmm for callers that have no way to provide scratch.
+ * (No counterpart in the reference, whose SpMM allocates its workspace itself.)
+ *
+ * Who needs it: a host that only forwards device pointers it was handed -- a
+ * cgo / JNI / ctypes binding without a device allocator of its own, or a
+ * serving process whose memory was reserved in full at start-up, where a
+ * cudaMalloc would fail or stall every stream with its implicit device
+ * synchronisation.  Such a caller can supply inputs and the output but not the
+ * hub-tier scratch that tgnn_workspace_bytes asks for.
+ *
+ * Here the hub-tier scratch is a fixed array of TGNN_STATIC_SCRATCH_BYTES that
+ * lives inside the library (each GPU that loads the library holds that much
+ * memory until the process exits).  `workspace` / `workspace_bytes` of the
+ * argument block are ignored.  The call allocates and frees nothing.
+ *   - A schedule whose hub tier needs more than TGNN_STATIC_SCRATCH_BYTES is
+ *     refused with TGNN_ERR_WORKSPACE and a message naming both sizes; use
+ *     tgnn_spmm with caller scratch, or larger hub chunks, in that case.
+ *   - The first call on each device looks up the device address of the array
+ *     (one runtime query, cached per device); make that first call outside any
+ *     stream capture.
+ *   - All calls on a device share the one array and it keeps the previous
+ *     call's contents.  Nothing in it has to start at zero: every hub chunk
+ *     writes its whole slot before the merge pass reads it.  Two calls that
+ *     overlap on the GPU (different streams) would overwrite each other's
+ *     partial results; issue them on one stream or order them with events. */
+#define TGNN_STATIC_SCRATCH_BYTES (8u << 20)
+int32_t tgnn_spmm_static_scratch(const tgnn_spmm_args *a);
+
 /* ---- attention: shared pieces -------------------------------------------- */
 
 /* Attention operands are [rows, heads*head_dim] matrices (a [N,H,D] tensor whose

@@ -275,6 +275,7 @@ ENTRY_POINTS = {
     "tgnn_segment_reduce_backward": SegmentReduceBwdArgs,
     "tgnn_degree_norm": DegreeNormArgs,
     "tgnn_spmm": SpmmArgs,
+    "tgnn_spmm_static_scratch": SpmmArgs,
     "tgnn_head_dot": HeadDotArgs,
     "tgnn_gatv2_forward": Gatv2FwdArgs,
     "tgnn_gatv2_backward_dst": Gatv2BwdDstArgs,

@@ -1,4 +1,6 @@
 // C-ABI entry points of the segment reductions and the weighted sum (g-SpMM).
+#include <mutex>
+
 #include "dispatch.cuh"
 #include "ops_reduce.cuh"
 
@@ -225,4 +227,56 @@ extern "C" int32_t tgnn_spmm(const tgnn_spmm_args *a) {
         return run_tiers<WeightedSumOp<T, I, kVpl, false>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
                                                            a->workspace_bytes, false);
     });
+}
+
+// ---- SpMM with library-owned scratch -----------------------------------------------------
+//
+// For hosts that cannot hand over scratch memory (they only forward pointers they were
+// given, or run with every byte of device memory already reserved).  The hub-tier
+// partials go to the fixed array below instead of caller memory.
+
+static __device__ __align__(256) unsigned char g_static_scratch[TGNN_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device
+// address, so the address is asked for once per device (with that device current)
+// and remembered.
+int32_t static_scratch_address(int device, void **out) {
+    static std::mutex mu;
+    static void *cached[64] = {nullptr};
+    TGNN_REQUIRE(device >= 0 && device < 64, TGNN_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", device);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[device] == nullptr) {
+        void *ptr = nullptr;
+        TGNN_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        TGNN_REQUIRE(ptr != nullptr, TGNN_ERR_CUDA, "static scratch has no device address");
+        cached[device] = ptr;
+    }
+    *out = cached[device];
+    return TGNN_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t tgnn_spmm_static_scratch(const tgnn_spmm_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));  // makes a->exec.device current before the address lookup
+    TGNN_REQUIRE(a->x.dtype == TGNN_F32 || a->x.dtype == TGNN_F16 || a->x.dtype == TGNN_BF16,
+                 TGNN_ERR_INVALID_ARGUMENT, "x: unknown element type %d", a->x.dtype);
+    TGNN_REQUIRE(a->csr.itype == TGNN_I32 || a->csr.itype == TGNN_I64, TGNN_ERR_INVALID_ARGUMENT,
+                 "unknown index type %d", a->csr.itype);
+    size_t need = 0;
+    if (a->sched.num_hub > 0 && a->sched.num_chunks > 0 && a->x.cols > 0)
+        need = reduce_scratch_bytes(TGNN_OP_WEIGHTED_SUM, a->x.dtype, a->csr.itype, a->sched.num_chunks, a->x.cols);
+    TGNN_REQUIRE(need <= static_cast<size_t>(TGNN_STATIC_SCRATCH_BYTES), TGNN_ERR_WORKSPACE,
+                 "hub tier needs %zu bytes of scratch but the built-in scratch holds %zu; "
+                 "call tgnn_spmm with caller scratch or use larger hub chunks",
+                 need, static_cast<size_t>(TGNN_STATIC_SCRATCH_BYTES));
+    void *scratch = nullptr;
+    TGNN_TRY(static_scratch_address(a->exec.device, &scratch));
+    tgnn_spmm_args with_scratch = *a;
+    with_scratch.workspace = scratch;
+    with_scratch.workspace_bytes = TGNN_STATIC_SCRATCH_BYTES;
+    return tgnn_spmm(&with_scratch);
 }
