@@ -98,7 +98,8 @@ typedef struct tgnn_schedule {
     int32_t chunk_edges;  /* edges per hub chunk, multiple of 32, 32..65536 */
     int32_t light_warps;  /* warps per CTA in the light tier: 1,2,4,8 */
     int32_t heavy_warps;  /* warps per CTA in the heavy and hub tiers: 1..16 */
-    int32_t _pad;
+    int32_t light_warps_per_row; /* 0 or 1: one warp per light row (light_warps rows per CTA);
+                                    2..16: light rows also get a CTA each, of this many warps */
 } tgnn_schedule;
 
 /* Row-major matrix view; `cols` contiguous elements per row. */

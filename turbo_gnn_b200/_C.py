@@ -27,6 +27,10 @@ import torch.nn.functional as F
 from . import _abi, _schedule
 
 _HEAD_DIMS = (16, 32, 64, 128, 256)
+# Rows per CTA in the warp-per-row tier of the attention ops.  The reference's
+# `*_light_warps` (1, 2, 4) means warps per light ROW; 1 selects the warp-per-row
+# tier, 2 and 4 give each light row a small CTA of its own.
+_LIGHT_CTA_WARPS = 4
 
 # Tunables of the hub tier that the reference signatures have no slot for.
 # `configure_hub_tier` changes them process-wide (the autotuner does).
@@ -517,7 +521,7 @@ def gatv2_forward(l, r, row_ptr, col_idx, attn_vec, negative_slope, light_nodes,
         args = _abi.Gatv2FwdArgs(
             exec=_abi.exec_of(l_in),
             csr=_abi.csr_of(row_ptr, col_idx, r.shape[0]),
-            sched=sched.to_struct(lw, hw),
+            sched=sched.to_struct(_LIGHT_CTA_WARPS, hw, lw),
             l=_abi.mat_of(l_in),
             r=_abi.mat_of(r_in),
             attn=_abi.ptr(a_in),
@@ -553,7 +557,7 @@ def gatv2_backward_dst(grad_h, l, r, row_ptr, col_idx, attn_vec, lse, G, negativ
         args = _abi.Gatv2BwdDstArgs(
             exec=_abi.exec_of(l_in),
             csr=_abi.csr_of(row_ptr, col_idx, r.shape[0]),
-            sched=sched.to_struct(_clamp_light(light_warps), _clamp_heavy(heavy_warps)),
+            sched=sched.to_struct(_LIGHT_CTA_WARPS, _clamp_heavy(heavy_warps), _clamp_light(light_warps)),
             grad_out=_abi.mat_of(g_in),
             l=_abi.mat_of(l_in),
             r=_abi.mat_of(r_in),
@@ -590,7 +594,7 @@ def gatv2_backward_src(grad_h, l, r, row_ptr_T, col_idx_T, attn_vec, lse, G, neg
         args = _abi.Gatv2BwdSrcArgs(
             exec=_abi.exec_of(r_in),
             csr_t=_abi.csr_of(row_ptr_T, col_idx_T, l.shape[0]),
-            sched=sched.to_struct(_clamp_light(light_warps), _clamp_heavy(heavy_warps)),
+            sched=sched.to_struct(_LIGHT_CTA_WARPS, _clamp_heavy(heavy_warps), _clamp_light(light_warps)),
             grad_out=_abi.mat_of(g_in),
             l=_abi.mat_of(l_in),
             r=_abi.mat_of(r_in),
@@ -664,7 +668,7 @@ def gt_forward_csr_mh(row_ptr, col_idx, Q, K, V, scale, light_nodes, heavy_nodes
         args = _abi.GtFwdArgs(
             exec=_abi.exec_of(q_in),
             csr=_abi.csr_of(row_ptr, col_idx, Q.shape[0]),
-            sched=sched.to_struct(lw, hw),
+            sched=sched.to_struct(_LIGHT_CTA_WARPS, hw, lw),
             q=_abi.mat_of(q_in),
             k=_abi.mat_of(k_in),
             v=_abi.mat_of(v_in),
@@ -693,7 +697,7 @@ def gt_backward_dst(row_ptr, col_idx, Q, K, V, dO, lse, delta, scale, light_node
         args = _abi.GtBwdDstArgs(
             exec=_abi.exec_of(k_in),
             csr=_abi.csr_of(row_ptr, col_idx, Q.shape[0]),
-            sched=sched.to_struct(_clamp_light(light_warps), _clamp_heavy(heavy_warps)),
+            sched=sched.to_struct(_LIGHT_CTA_WARPS, _clamp_heavy(heavy_warps), _clamp_light(light_warps)),
             q=_abi.mat_of(q_in),
             k=_abi.mat_of(k_in),
             v=_abi.mat_of(v_in),
@@ -728,7 +732,7 @@ def gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_
         args = _abi.GtBwdSrcArgs(
             exec=_abi.exec_of(q_in),
             csr_t=_abi.csr_of(row_ptr_T, col_idx_T, K.shape[0]),
-            sched=sched.to_struct(_clamp_light(light_warps), _clamp_heavy(heavy_warps)),
+            sched=sched.to_struct(_LIGHT_CTA_WARPS, _clamp_heavy(heavy_warps), _clamp_light(light_warps)),
             q=_abi.mat_of(q_in),
             k=_abi.mat_of(k_in),
             v=_abi.mat_of(v_in),

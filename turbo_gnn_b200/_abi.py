@@ -63,7 +63,7 @@ class Schedule(C.Structure):
         ("chunk_edges", C.c_int32),
         ("light_warps", C.c_int32),
         ("heavy_warps", C.c_int32),
-        ("_pad", C.c_int32),
+        ("light_warps_per_row", C.c_int32),
     ]
 
 

@@ -39,8 +39,11 @@ class TierSchedule:
     num_chunks: int
     chunk_edges: int
 
-    def to_struct(self, light_warps: int, heavy_warps: int) -> _abi.Schedule:
+    def to_struct(self, light_warps: int, heavy_warps: int, light_warps_per_row: int = 1) -> _abi.Schedule:
+        """`light_warps` rows share a CTA in the warp-per-row tier; `light_warps_per_row` > 1 gives
+        each light row a CTA of that many warps instead."""
         return _abi.Schedule(
+            light_warps_per_row=int(light_warps_per_row),
             light_rows=_abi.ptr(self.light),
             num_light=self.light.numel(),
             heavy_rows=_abi.ptr(self.heavy),

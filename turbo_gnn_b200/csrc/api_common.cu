@@ -50,9 +50,13 @@ int32_t check_schedule(const tgnn_schedule &s, const tgnn_csr &c) {
     TGNN_REQUIRE(s.num_heavy == 0 || s.heavy_rows != nullptr, TGNN_ERR_INVALID_ARGUMENT, "heavy_rows is null");
     TGNN_REQUIRE(s.num_light <= c.num_rows && s.num_heavy <= c.num_rows && s.num_hub <= c.num_rows,
                  TGNN_ERR_INVALID_ARGUMENT, "a row list is longer than the CSR has rows");
-    if (s.num_light > 0)
-        TGNN_REQUIRE(s.light_warps == 1 || s.light_warps == 2 || s.light_warps == 4 || s.light_warps == 8,
-                     TGNN_ERR_LAUNCH_PARAM, "Wrong int value: light warps %d not in {1,2,4,8}", s.light_warps);
+    if (s.num_light > 0) {
+        TGNN_REQUIRE(s.light_warps_per_row >= 0 && s.light_warps_per_row <= 16, TGNN_ERR_LAUNCH_PARAM,
+                     "Wrong int value: warps per light row %d not in 0..16", s.light_warps_per_row);
+        if (s.light_warps_per_row <= 1)
+            TGNN_REQUIRE(s.light_warps == 1 || s.light_warps == 2 || s.light_warps == 4 || s.light_warps == 8,
+                         TGNN_ERR_LAUNCH_PARAM, "Wrong int value: light warps %d not in {1,2,4,8}", s.light_warps);
+    }
     if (s.num_heavy > 0 || s.num_hub > 0)
         TGNN_REQUIRE(s.heavy_warps >= 1 && s.heavy_warps <= 16, TGNN_ERR_LAUNCH_PARAM,
                      "Wrong int value: heavy warps %d not in 1..16", s.heavy_warps);

@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(256) head_dot_kernel(const T *__restrict__ a, 
     L.g_lane = L.lane;
     L.grp = 0;
     L.ngrp = 1;
-    const ChunkMap<kVpl, kPer> map(L, cols);
+    const AttnMap<kVpl, kPer> map(L, cols);
     const HeadMap<kVpl, kPer> hm(L, map, head_dim);
     const int warps = blockDim.x >> 5;
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); row < rows;

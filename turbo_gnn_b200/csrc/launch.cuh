@@ -80,7 +80,18 @@ int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_
     CsrDev<I> c{static_cast<const I *>(csr.indptr), static_cast<const I *>(csr.indices)};
     const int carry_smem = Op::kCarryWords * 32 * static_cast<int>(sizeof(uint32_t));
 
-    if (s.num_light > 0) {
+    HubDev<I> no_hub{nullptr, nullptr, nullptr, 0};
+    if (s.num_light > 0 && s.light_warps_per_row > 1) {
+        // Light rows as CTA-per-row with a small CTA (the reference's "warps per light row").
+        const int lw = s.light_warps_per_row;
+        const size_t smem = static_cast<size_t>(lw - 1) * Op::kWords * 32 * sizeof(uint32_t);
+        dim3 grid(static_cast<unsigned>(s.num_light), geo.slices);
+        auto k = sweep_heavy_kernel<Op, false>;
+        if (smem > 48 * 1024)
+            TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<grid, lw * 32, smem, stream>>>(p, c, static_cast<const I *>(s.light_rows), no_hub, nullptr, geo.G);
+        TGNN_CUDA(cudaGetLastError());
+    } else if (s.num_light > 0) {
         const int warps = s.light_warps;
         int64_t blocks = (s.num_light + warps - 1) / warps;
         if (persistent_light) {

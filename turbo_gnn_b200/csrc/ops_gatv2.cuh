@@ -34,8 +34,14 @@ struct Gatv2Params {
     float slope;
 };
 
-__device__ __forceinline__ float lrelu(float z, float slope) { return z > 0.0f ? z : z * slope; }
-__device__ __forceinline__ float lrelu_grad(float z, float slope) { return z > 0.0f ? 1.0f : slope; }
+// LReLU(z) = z + (slope - 1) * min(z, 0): two instructions, no select.
+__device__ __forceinline__ float lrelu(float z, float slope_m1) { return fmaf(fminf(z, 0.0f), slope_m1, z); }
+
+template <int kVpl>
+__device__ __forceinline__ void clear_frag(uint4 (&raw)[kVpl]) {
+#pragma unroll
+    for (int v = 0; v < kVpl; ++v) raw[v] = make_uint4(0u, 0u, 0u, 0u);
+}
 
 // ---- forward ----------------------------------------------------------------------
 template <typename T, typename I, int kVpl>
@@ -60,14 +66,18 @@ struct Gatv2FwdOp {
 
     const Params &p;
     const Lanes &L;
-    ChunkMap<kVpl, kPer> map;
+    AttnMap<kVpl, kPer> map;
     HeadMap<kVpl, kPer> hm;
     uint64_t keep;
-    float a[kVals];
+    float slope_m1;
+    float a[kVals];  // attention vector times log2(e): scores come out in the base-2 domain
 
     __device__ __forceinline__ Gatv2FwdOp(const Params &p_, const Lanes &L_)
-        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {
+        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()),
+          slope_m1(p_.slope - 1.0f) {
         load_row_f32<T, kVpl>(p.attn, map, a);
+#pragma unroll
+        for (int i = 0; i < kVals; ++i) a[i] *= kLog2e;
     }
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
         load_row_f32<T, kVpl>(p.l + static_cast<int64_t>(row) * p.ldl, map, rc.l);
@@ -76,27 +86,35 @@ struct Gatv2FwdOp {
     __device__ __forceinline__ void load(I src, Frag &f) {
         gather_row<T, kVpl>(p.r + static_cast<int64_t>(src) * p.ldr, map, keep, f.raw);
     }
-    __device__ __forceinline__ void consume(const Row &rc, State &s, const Frag &f, I, I, bool valid) {
-        float pv[kVpl];
+    template <bool kAll>
+    __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
+                                            const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
+        float sc[kUnroll * kVpl];
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            pv[v] = 0.0f;
-            if (valid && map.off[v] >= 0) {
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!kAll && !ok[u]) clear_frag<kVpl>(f[u].raw);
+#pragma unroll
+            for (int v = 0; v < kVpl; ++v) {
                 float x[kPer];
-                Elem<T>::unpack(f.raw[v], x);
+                Elem<T>::unpack(f[u].raw[v], x);
+                float acc = 0.0f;
 #pragma unroll
                 for (int e = 0; e < kPer; ++e)
-                    pv[v] = fmaf(a[v * kPer + e], lrelu(rc.l[v * kPer + e] + x[e], p.slope), pv[v]);
+                    acc = fmaf(a[v * kPer + e], lrelu(rc.l[v * kPer + e] + x[e], slope_m1), acc);
+                sc[u * kVpl + v] = acc;
             }
         }
-        hm.finish(pv);
-        if (!valid) return;
+        hm.finish(sc);
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
-            float x[kPer];
-            Elem<T>::unpack(f.raw[v], x);
-            s.push(v, pv[v], x);
+            float s2[kUnroll];
+            float x[kUnroll][kPer];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                s2[u] = (kAll || ok[u]) ? sc[u * kVpl + v] : -INFINITY;
+                Elem<T>::unpack(f[u].raw[v], x[u]);
+            }
+            s.template push<kUnroll, kAll>(v, s2, x);
         }
     }
     __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
@@ -107,15 +125,13 @@ struct Gatv2FwdOp {
         T *orow = p.out + static_cast<int64_t>(row) * p.ldo;
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
+            if (!map.live[v]) continue;
             const float inv = s.s[v] > 0.0f ? 1.0f / s.s[v] : 0.0f;
             float x[kPer];
 #pragma unroll
             for (int e = 0; e < kPer; ++e) x[e] = s.acc[v * kPer + e] * inv;
             st_stream16(orow + map.off[v], Elem<T>::pack(x));
-            if (hm.writer[v])
-                p.lse_out[static_cast<int64_t>(row) * p.heads + hm.head[v]] =
-                    s.s[v] > 0.0f ? s.m[v] + __logf(s.s[v]) : -INFINITY;
+            if (hm.writer[v]) p.lse_out[static_cast<int64_t>(row) * p.heads + hm.head[v]] = s.lse(v);
         }
     }
     __device__ __forceinline__ void flush_row(State &) {}
@@ -138,7 +154,7 @@ struct Gatv2BwdDstOp {
     struct Row {
         float l[kVals];
         float gh[kVals];
-        float lse[kVpl];
+        float lse2[kVpl];  // log-sum-exp in the base-2 domain
         float G[kVpl];
     };
     using State = SumAcc<2 * kVals>;
@@ -151,13 +167,15 @@ struct Gatv2BwdDstOp {
 
     const Params &p;
     const Lanes &L;
-    ChunkMap<kVpl, kPer> map;
+    AttnMap<kVpl, kPer> map;
     HeadMap<kVpl, kPer> hm;
     uint64_t keep;
+    float slope_m1;
     float a[kVals];
 
     __device__ __forceinline__ Gatv2BwdDstOp(const Params &p_, const Lanes &L_)
-        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {
+        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()),
+          slope_m1(p_.slope - 1.0f) {
         load_row_f32<T, kVpl>(p.attn, map, a);
     }
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
@@ -165,8 +183,8 @@ struct Gatv2BwdDstOp {
         load_row_f32<T, kVpl>(p.gh + static_cast<int64_t>(row) * p.ldg, map, rc.gh);
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            const int64_t at = static_cast<int64_t>(row) * p.heads + (hm.head[v] >= 0 ? hm.head[v] : 0);
-            rc.lse[v] = __ldg(p.lse + at);
+            const int64_t at = static_cast<int64_t>(row) * p.heads + hm.head[v];
+            rc.lse2[v] = __ldg(p.lse + at) * kLog2e;
             rc.G[v] = __ldg(p.G + at);
         }
     }
@@ -174,39 +192,46 @@ struct Gatv2BwdDstOp {
     __device__ __forceinline__ void load(I src, Frag &f) {
         gather_row<T, kVpl>(p.r + static_cast<int64_t>(src) * p.ldr, map, keep, f.raw);
     }
-    __device__ __forceinline__ void consume(const Row &rc, State &s, const Frag &f, I, I, bool valid) {
-        float pe[kVpl], pp[kVpl];
+    template <bool kAll>
+    __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
+                                            const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
+        float d[2 * kUnroll * kVpl];  // [edge score | <gh, r>] partial dot products
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            pe[v] = 0.0f;
-            pp[v] = 0.0f;
-            if (valid && map.off[v] >= 0) {
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!kAll && !ok[u]) clear_frag<kVpl>(f[u].raw);
+#pragma unroll
+            for (int v = 0; v < kVpl; ++v) {
                 float x[kPer];
-                Elem<T>::unpack(f.raw[v], x);
+                Elem<T>::unpack(f[u].raw[v], x);
+                float pe = 0.0f, pp = 0.0f;
 #pragma unroll
                 for (int e = 0; e < kPer; ++e) {
                     const int i = v * kPer + e;
-                    pe[v] = fmaf(a[i], lrelu(rc.l[i] + x[e], p.slope), pe[v]);
-                    pp[v] = fmaf(rc.gh[i], x[e], pp[v]);
+                    pe = fmaf(a[i], lrelu(rc.l[i] + x[e], slope_m1), pe);
+                    pp = fmaf(rc.gh[i], x[e], pp);
                 }
+                d[u * kVpl + v] = pe;
+                d[(kUnroll + u) * kVpl + v] = pp;
             }
         }
-        hm.finish(pe);
-        hm.finish(pp);
-        if (!valid) return;
+        hm.finish(d);
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
-            const float alpha = __expf(pe[v] - rc.lse[v]);
-            const float ge = alpha * (pp[v] - rc.G[v]);
-            float x[kPer];
-            Elem<T>::unpack(f.raw[v], x);
+        for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) {
-                const int i = v * kPer + e;
-                const float z = rc.l[i] + x[e];
-                s.a[i] = fmaf(ge * lrelu_grad(z, p.slope), a[i], s.a[i]);
-                s.a[kVals + i] = fmaf(ge, lrelu(z, p.slope), s.a[kVals + i]);
+            for (int v = 0; v < kVpl; ++v) {
+                float alpha = fast_exp2(fmaf(d[u * kVpl + v], kLog2e, -rc.lse2[v]));
+                if (!kAll && !ok[u]) alpha = 0.0f;
+                const float ge = alpha * (d[(kUnroll + u) * kVpl + v] - rc.G[v]);
+                const float ge_neg = ge * p.slope;
+                float x[kPer];
+                Elem<T>::unpack(f[u].raw[v], x);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    const int i = v * kPer + e;
+                    const float z = rc.l[i] + x[e];
+                    s.a[i] = fmaf(z > 0.0f ? ge : ge_neg, a[i], s.a[i]);
+                    s.a[kVals + i] = fmaf(ge, lrelu(z, slope_m1), s.a[kVals + i]);
+                }
             }
         }
     }
@@ -222,7 +247,7 @@ struct Gatv2BwdDstOp {
         if (L.grp != 0) return;
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
+            if (!map.live[v]) continue;
 #pragma unroll
             for (int e = 0; e < kPer; ++e) atomicAdd(p.grad_attn + map.off[v] + e, s.a[kVals + v * kPer + e]);
         }
@@ -247,7 +272,7 @@ struct Gatv2BwdDstOp {
         if (warp != 0 || L.grp != 0) return;
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
+            if (!map.live[v]) continue;
 #pragma unroll
             for (int e = 0; e < kPer; ++e) {
                 const int i = v * kPer + e;
@@ -284,13 +309,15 @@ struct Gatv2BwdSrcOp {
 
     const Params &p;
     const Lanes &L;
-    ChunkMap<kVpl, kPer> map;
+    AttnMap<kVpl, kPer> map;
     HeadMap<kVpl, kPer> hm;
     uint64_t keep;
+    float slope_m1;
     float a[kVals];
 
     __device__ __forceinline__ Gatv2BwdSrcOp(const Params &p_, const Lanes &L_)
-        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {
+        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()),
+          slope_m1(p_.slope - 1.0f) {
         load_row_f32<T, kVpl>(p.attn, map, a);
     }
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
@@ -302,45 +329,57 @@ struct Gatv2BwdSrcOp {
         gather_row<T, kVpl>(p.gh + static_cast<int64_t>(dst) * p.ldg, map, keep, f.rawg);
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            const int64_t at = static_cast<int64_t>(dst) * p.heads + (hm.head[v] >= 0 ? hm.head[v] : 0);
+            const int64_t at = static_cast<int64_t>(dst) * p.heads + hm.head[v];
             f.lse[v] = __ldg(p.lse + at);
             f.G[v] = __ldg(p.G + at);
         }
     }
-    __device__ __forceinline__ void consume(const Row &rc, State &s, const Frag &f, I, I, bool valid) {
-        float pe[kVpl], pp[kVpl];
+    template <bool kAll>
+    __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
+                                            const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
+        float d[2 * kUnroll * kVpl];
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            pe[v] = 0.0f;
-            pp[v] = 0.0f;
-            if (valid && map.off[v] >= 0) {
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!kAll && !ok[u]) {
+                clear_frag<kVpl>(f[u].rawl);
+                clear_frag<kVpl>(f[u].rawg);
+#pragma unroll
+                for (int v = 0; v < kVpl; ++v) f[u].lse[v] = f[u].G[v] = 0.0f;
+            }
+#pragma unroll
+            for (int v = 0; v < kVpl; ++v) {
                 float xl[kPer], xg[kPer];
-                Elem<T>::unpack(f.rawl[v], xl);
-                Elem<T>::unpack(f.rawg[v], xg);
+                Elem<T>::unpack(f[u].rawl[v], xl);
+                Elem<T>::unpack(f[u].rawg[v], xg);
+                float pe = 0.0f, pp = 0.0f;
 #pragma unroll
                 for (int e = 0; e < kPer; ++e) {
                     const int i = v * kPer + e;
-                    pe[v] = fmaf(a[i], lrelu(xl[e] + rc.r[i], p.slope), pe[v]);
-                    pp[v] = fmaf(xg[e], rc.r[i], pp[v]);
+                    pe = fmaf(a[i], lrelu(xl[e] + rc.r[i], slope_m1), pe);
+                    pp = fmaf(xg[e], rc.r[i], pp);
                 }
+                d[u * kVpl + v] = pe;
+                d[(kUnroll + u) * kVpl + v] = pp;
             }
         }
-        hm.finish(pe);
-        hm.finish(pp);
-        if (!valid) return;
+        hm.finish(d);
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
-            const float alpha = __expf(pe[v] - f.lse[v]);
-            const float ge = alpha * (pp[v] - f.G[v]);
-            float xl[kPer], xg[kPer];
-            Elem<T>::unpack(f.rawl[v], xl);
-            Elem<T>::unpack(f.rawg[v], xg);
+        for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) {
-                const int i = v * kPer + e;
-                const float z = xl[e] + rc.r[i];
-                s.a[i] = fmaf(alpha, xg[e], fmaf(ge * lrelu_grad(z, p.slope), a[i], s.a[i]));
+            for (int v = 0; v < kVpl; ++v) {
+                float alpha = fast_exp2((d[u * kVpl + v] - f[u].lse[v]) * kLog2e);
+                if (!kAll && !ok[u]) alpha = 0.0f;
+                const float ge = alpha * (d[(kUnroll + u) * kVpl + v] - f[u].G[v]);
+                const float ge_neg = ge * p.slope;
+                float xl[kPer], xg[kPer];
+                Elem<T>::unpack(f[u].rawl[v], xl);
+                Elem<T>::unpack(f[u].rawg[v], xg);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    const int i = v * kPer + e;
+                    const float z = xl[e] + rc.r[i];
+                    s.a[i] = fmaf(alpha, xg[e], fmaf(z > 0.0f ? ge : ge_neg, a[i], s.a[i]));
+                }
             }
         }
     }

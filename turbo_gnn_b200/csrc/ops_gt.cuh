@@ -36,6 +36,12 @@ struct GtParams {
     float scale;
 };
 
+template <int kVpl>
+__device__ __forceinline__ void clear_chunks(uint4 (&raw)[kVpl]) {
+#pragma unroll
+    for (int v = 0; v < kVpl; ++v) raw[v] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 // ---- forward ----------------------------------------------------------------------
 template <typename T, typename I, int kVpl>
 struct GtFwdOp {
@@ -49,7 +55,7 @@ struct GtFwdOp {
     static constexpr int kCarryWords = 0;
 
     struct Row {
-        float k[kVals];
+        float k[kVals];  // key row times scale * log2(e)
     };
     using State = Acc;
     using Carry = NoCarry;
@@ -60,7 +66,7 @@ struct GtFwdOp {
 
     const Params &p;
     const Lanes &L;
-    ChunkMap<kVpl, kPer> map;
+    AttnMap<kVpl, kPer> map;
     HeadMap<kVpl, kPer> hm;
     uint64_t keep;
 
@@ -68,34 +74,46 @@ struct GtFwdOp {
         : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {}
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
         load_row_f32<T, kVpl>(p.k + static_cast<int64_t>(row) * p.ldk, map, rc.k);
+        const float f = p.scale * kLog2e;
 #pragma unroll
-        for (int i = 0; i < kVals; ++i) rc.k[i] *= p.scale;
+        for (int i = 0; i < kVals; ++i) rc.k[i] *= f;
     }
     __device__ __forceinline__ void init(State &s) { s.init(); }
     __device__ __forceinline__ void load(I src, Frag &f) {
         gather_row<T, kVpl>(p.q + static_cast<int64_t>(src) * p.ldq, map, keep, f.rawq);
         gather_row<T, kVpl>(p.v + static_cast<int64_t>(src) * p.ldv, map, keep, f.rawv);
     }
-    __device__ __forceinline__ void consume(const Row &rc, State &s, const Frag &f, I, I, bool valid) {
-        float pv[kVpl];
+    template <bool kAll>
+    __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
+                                            const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
+        float sc[kUnroll * kVpl];
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            pv[v] = 0.0f;
-            if (valid && map.off[v] >= 0) {
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!kAll && !ok[u]) {
+                clear_chunks<kVpl>(f[u].rawq);
+                clear_chunks<kVpl>(f[u].rawv);
+            }
+#pragma unroll
+            for (int v = 0; v < kVpl; ++v) {
                 float x[kPer];
-                Elem<T>::unpack(f.rawq[v], x);
+                Elem<T>::unpack(f[u].rawq[v], x);
+                float acc = 0.0f;
 #pragma unroll
-                for (int e = 0; e < kPer; ++e) pv[v] = fmaf(x[e], rc.k[v * kPer + e], pv[v]);
+                for (int e = 0; e < kPer; ++e) acc = fmaf(x[e], rc.k[v * kPer + e], acc);
+                sc[u * kVpl + v] = acc;
             }
         }
-        hm.finish(pv);
-        if (!valid) return;
+        hm.finish(sc);
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
-            float x[kPer];
-            Elem<T>::unpack(f.rawv[v], x);
-            s.push(v, pv[v], x);
+            float s2[kUnroll];
+            float x[kUnroll][kPer];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                s2[u] = (kAll || ok[u]) ? sc[u * kVpl + v] : -INFINITY;
+                Elem<T>::unpack(f[u].rawv[v], x[u]);
+            }
+            s.template push<kUnroll, kAll>(v, s2, x);
         }
     }
     __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
@@ -106,15 +124,13 @@ struct GtFwdOp {
         T *orow = p.out0 + static_cast<int64_t>(row) * p.ldo0;
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
+            if (!map.live[v]) continue;
             const float inv = s.s[v] > 0.0f ? 1.0f / s.s[v] : 0.0f;
             float x[kPer];
 #pragma unroll
             for (int e = 0; e < kPer; ++e) x[e] = s.acc[v * kPer + e] * inv;
             st_stream16(orow + map.off[v], Elem<T>::pack(x));
-            if (hm.writer[v])
-                p.lse_out[static_cast<int64_t>(row) * p.heads + hm.head[v]] =
-                    s.s[v] > 0.0f ? s.m[v] + __logf(s.s[v]) : -INFINITY;
+            if (hm.writer[v]) p.lse_out[static_cast<int64_t>(row) * p.heads + hm.head[v]] = s.lse(v);
         }
     }
     __device__ __forceinline__ void flush_row(State &) {}
@@ -135,9 +151,9 @@ struct GtBwdDstOp {
     static constexpr int kCarryWords = 0;
 
     struct Row {
-        float k[kVals];   // pre-scaled
+        float k[kVals];  // times scale * log2(e)
         float dO[kVals];
-        float lse[kVpl];
+        float lse2[kVpl];
         float delta[kVpl];
     };
     using State = SumAcc<kVals>;
@@ -149,7 +165,7 @@ struct GtBwdDstOp {
 
     const Params &p;
     const Lanes &L;
-    ChunkMap<kVpl, kPer> map;
+    AttnMap<kVpl, kPer> map;
     HeadMap<kVpl, kPer> hm;
     uint64_t keep;
 
@@ -158,12 +174,13 @@ struct GtBwdDstOp {
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
         load_row_f32<T, kVpl>(p.k + static_cast<int64_t>(row) * p.ldk, map, rc.k);
         load_row_f32<T, kVpl>(p.d_out + static_cast<int64_t>(row) * p.ldd, map, rc.dO);
+        const float f = p.scale * kLog2e;
 #pragma unroll
-        for (int i = 0; i < kVals; ++i) rc.k[i] *= p.scale;
+        for (int i = 0; i < kVals; ++i) rc.k[i] *= f;
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            const int64_t at = static_cast<int64_t>(row) * p.heads + (hm.head[v] >= 0 ? hm.head[v] : 0);
-            rc.lse[v] = __ldg(p.lse + at);
+            const int64_t at = static_cast<int64_t>(row) * p.heads + hm.head[v];
+            rc.lse2[v] = __ldg(p.lse + at) * kLog2e;
             rc.delta[v] = __ldg(p.delta + at);
         }
     }
@@ -172,35 +189,44 @@ struct GtBwdDstOp {
         gather_row<T, kVpl>(p.q + static_cast<int64_t>(src) * p.ldq, map, keep, f.rawq);
         gather_row<T, kVpl>(p.v + static_cast<int64_t>(src) * p.ldv, map, keep, f.rawv);
     }
-    __device__ __forceinline__ void consume(const Row &rc, State &s, const Frag &f, I, I, bool valid) {
-        float ps[kVpl], pd[kVpl];
+    template <bool kAll>
+    __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
+                                            const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
+        float d[2 * kUnroll * kVpl];
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            ps[v] = 0.0f;
-            pd[v] = 0.0f;
-            if (valid && map.off[v] >= 0) {
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!kAll && !ok[u]) {
+                clear_chunks<kVpl>(f[u].rawq);
+                clear_chunks<kVpl>(f[u].rawv);
+            }
+#pragma unroll
+            for (int v = 0; v < kVpl; ++v) {
                 float xq[kPer], xv[kPer];
-                Elem<T>::unpack(f.rawq[v], xq);
-                Elem<T>::unpack(f.rawv[v], xv);
+                Elem<T>::unpack(f[u].rawq[v], xq);
+                Elem<T>::unpack(f[u].rawv[v], xv);
+                float ps = 0.0f, pd = 0.0f;
 #pragma unroll
                 for (int e = 0; e < kPer; ++e) {
-                    ps[v] = fmaf(xq[e], rc.k[v * kPer + e], ps[v]);
-                    pd[v] = fmaf(xv[e], rc.dO[v * kPer + e], pd[v]);
+                    ps = fmaf(xq[e], rc.k[v * kPer + e], ps);
+                    pd = fmaf(xv[e], rc.dO[v * kPer + e], pd);
                 }
+                d[u * kVpl + v] = ps;
+                d[(kUnroll + u) * kVpl + v] = pd;
             }
         }
-        hm.finish(ps);
-        hm.finish(pd);
-        if (!valid) return;
+        hm.finish(d);
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
-            const float alpha = __expf(ps[v] - rc.lse[v]);
-            const float ds = alpha * (pd[v] - rc.delta[v]) * p.scale;
-            float xq[kPer];
-            Elem<T>::unpack(f.rawq[v], xq);
+        for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) s.a[v * kPer + e] = fmaf(ds, xq[e], s.a[v * kPer + e]);
+            for (int v = 0; v < kVpl; ++v) {
+                float alpha = fast_exp2(d[u * kVpl + v] - rc.lse2[v]);
+                if (!kAll && !ok[u]) alpha = 0.0f;
+                const float ds = alpha * (d[(kUnroll + u) * kVpl + v] - rc.delta[v]) * p.scale;
+                float xq[kPer];
+                Elem<T>::unpack(f[u].rawq[v], xq);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) s.a[v * kPer + e] = fmaf(ds, xq[e], s.a[v * kPer + e]);
+            }
         }
     }
     __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
@@ -228,7 +254,7 @@ struct GtBwdSrcOp {
     static constexpr int kCarryWords = 0;
 
     struct Row {
-        float q[kVals];  // pre-scaled
+        float q[kVals];  // times scale * log2(e)
         float v[kVals];
     };
     using State = SumAcc<2 * kVals>;
@@ -242,7 +268,7 @@ struct GtBwdSrcOp {
 
     const Params &p;
     const Lanes &L;
-    ChunkMap<kVpl, kPer> map;
+    AttnMap<kVpl, kPer> map;
     HeadMap<kVpl, kPer> hm;
     uint64_t keep;
 
@@ -251,8 +277,9 @@ struct GtBwdSrcOp {
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
         load_row_f32<T, kVpl>(p.q + static_cast<int64_t>(row) * p.ldq, map, rc.q);
         load_row_f32<T, kVpl>(p.v + static_cast<int64_t>(row) * p.ldv, map, rc.v);
+        const float f = p.scale * kLog2e;
 #pragma unroll
-        for (int i = 0; i < kVals; ++i) rc.q[i] *= p.scale;
+        for (int i = 0; i < kVals; ++i) rc.q[i] *= f;
     }
     __device__ __forceinline__ void init(State &s) { s.init(); }
     __device__ __forceinline__ void load(I dst, Frag &f) {
@@ -260,44 +287,55 @@ struct GtBwdSrcOp {
         gather_row<T, kVpl>(p.d_out + static_cast<int64_t>(dst) * p.ldd, map, keep, f.rawd);
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            const int64_t at = static_cast<int64_t>(dst) * p.heads + (hm.head[v] >= 0 ? hm.head[v] : 0);
+            const int64_t at = static_cast<int64_t>(dst) * p.heads + hm.head[v];
             f.lse[v] = __ldg(p.lse + at);
             f.delta[v] = __ldg(p.delta + at);
         }
     }
-    __device__ __forceinline__ void consume(const Row &rc, State &s, const Frag &f, I, I, bool valid) {
-        float ps[kVpl], pd[kVpl];
+    template <bool kAll>
+    __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
+                                            const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
+        float d[2 * kUnroll * kVpl];
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            ps[v] = 0.0f;
-            pd[v] = 0.0f;
-            if (valid && map.off[v] >= 0) {
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!kAll && !ok[u]) {
+                clear_chunks<kVpl>(f[u].rawk);
+                clear_chunks<kVpl>(f[u].rawd);
+#pragma unroll
+                for (int v = 0; v < kVpl; ++v) f[u].lse[v] = f[u].delta[v] = 0.0f;
+            }
+#pragma unroll
+            for (int v = 0; v < kVpl; ++v) {
                 float xk[kPer], xd[kPer];
-                Elem<T>::unpack(f.rawk[v], xk);
-                Elem<T>::unpack(f.rawd[v], xd);
+                Elem<T>::unpack(f[u].rawk[v], xk);
+                Elem<T>::unpack(f[u].rawd[v], xd);
+                float ps = 0.0f, pd = 0.0f;
 #pragma unroll
                 for (int e = 0; e < kPer; ++e) {
-                    ps[v] = fmaf(xk[e], rc.q[v * kPer + e], ps[v]);
-                    pd[v] = fmaf(xd[e], rc.v[v * kPer + e], pd[v]);
+                    ps = fmaf(xk[e], rc.q[v * kPer + e], ps);
+                    pd = fmaf(xd[e], rc.v[v * kPer + e], pd);
                 }
+                d[u * kVpl + v] = ps;
+                d[(kUnroll + u) * kVpl + v] = pd;
             }
         }
-        hm.finish(ps);
-        hm.finish(pd);
-        if (!valid) return;
+        hm.finish(d);
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
-            const float alpha = __expf(ps[v] - f.lse[v]);
-            const float ds = alpha * (pd[v] - f.delta[v]) * p.scale;
-            float xk[kPer], xd[kPer];
-            Elem<T>::unpack(f.rawk[v], xk);
-            Elem<T>::unpack(f.rawd[v], xd);
+        for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) {
-                const int i = v * kPer + e;
-                s.a[i] = fmaf(ds, xk[e], s.a[i]);
-                s.a[kVals + i] = fmaf(alpha, xd[e], s.a[kVals + i]);
+            for (int v = 0; v < kVpl; ++v) {
+                float alpha = fast_exp2(fmaf(-f[u].lse[v], kLog2e, d[u * kVpl + v]));
+                if (!kAll && !ok[u]) alpha = 0.0f;
+                const float ds = alpha * (d[(kUnroll + u) * kVpl + v] - f[u].delta[v]) * p.scale;
+                float xk[kPer], xd[kPer];
+                Elem<T>::unpack(f[u].rawk[v], xk);
+                Elem<T>::unpack(f[u].rawd[v], xd);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    const int i = v * kPer + e;
+                    s.a[i] = fmaf(ds, xk[e], s.a[i]);
+                    s.a[kVals + i] = fmaf(alpha, xd[e], s.a[kVals + i]);
+                }
             }
         }
     }

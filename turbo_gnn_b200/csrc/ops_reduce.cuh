@@ -83,20 +83,25 @@ struct MinMaxOp {
         for (int v = 0; v < kVpl; ++v)
             if (map.off[v] >= 0) f.raw[v] = ld_gather16(row + map.off[v], keep);
     }
-    __device__ __forceinline__ void consume(const Row &, State &s, const Frag &f, I src, I, bool valid) {
-        if (!valid) return;
+    template <bool kAll>
+    __device__ __forceinline__ void consume(const Row &, State &s, const Frag (&f)[kUnroll], const I (&src)[kUnroll],
+                                            const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
-            float x[kPer];
-            Elem<T>::unpack(f.raw[v], x);
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!kAll && !ok[u]) continue;
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) {
-                const int i = v * kPer + e;
-                const bool take = better(x[e], s.val[i]) || (x[e] == s.val[i] && src < s.idx[i]);
-                if (take) {
-                    s.val[i] = x[e];
-                    s.idx[i] = src;
+            for (int v = 0; v < kVpl; ++v) {
+                if (map.off[v] < 0) continue;
+                float x[kPer];
+                Elem<T>::unpack(f[u].raw[v], x);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    const int i = v * kPer + e;
+                    const bool take = better(x[e], s.val[i]) || (x[e] == s.val[i] && src[u] < s.idx[i]);
+                    if (take) {
+                        s.val[i] = x[e];
+                        s.idx[i] = src[u];
+                    }
                 }
             }
         }
@@ -219,24 +224,29 @@ struct WeightedSumOp {
             if (map.off[v] >= 0) f.raw[v] = ld_gather16(row + map.off[v], keep);
         if (kWeighted) f.w = p.col_scale != nullptr ? __ldg(p.col_scale + src) : 1.0f;
     }
-    __device__ __forceinline__ void consume(const Row &, State &s, const Frag &f, I, I eid, bool valid) {
-        if (!valid) return;
-        float w = 1.0f;
-        if (kWeighted) {
-            w = f.w;
-            if (p.edge_weight != nullptr) w *= __ldg(p.edge_weight + eid);
-        }
+    template <bool kAll>
+    __device__ __forceinline__ void consume(const Row &, State &s, const Frag (&f)[kUnroll], const I (&)[kUnroll],
+                                            const I (&eid)[kUnroll], const bool (&ok)[kUnroll]) {
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
-            float x[kPer];
-            Elem<T>::unpack(f.raw[v], x);
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!kAll && !ok[u]) continue;
+            float w = 1.0f;
+            if (kWeighted) {
+                w = f[u].w;
+                if (p.edge_weight != nullptr) w *= __ldg(p.edge_weight + eid[u]);
+            }
 #pragma unroll
-            for (int e = 0; e < kPer; ++e) {
-                if (kWeighted)
-                    s.acc[v * kPer + e] = fmaf(w, x[e], s.acc[v * kPer + e]);
-                else
-                    s.acc[v * kPer + e] += x[e];
+            for (int v = 0; v < kVpl; ++v) {
+                if (map.off[v] < 0) continue;
+                float x[kPer];
+                Elem<T>::unpack(f[u].raw[v], x);
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) {
+                    if (kWeighted)
+                        s.acc[v * kPer + e] = fmaf(w, x[e], s.acc[v * kPer + e]);
+                    else
+                        s.acc[v * kPer + e] += x[e];
+                }
             }
         }
     }

@@ -16,7 +16,9 @@
 //
 // Column indices are read once per warp as a coalesced 32-wide block, the next
 // block is prefetched into registers while the current one is processed, and
-// single indices are handed out by shuffle.
+// single indices are handed out by shuffle.  Edges reach the op in batches of
+// Op::kUnroll per lane group (all gathers of a batch are issued before any is
+// consumed); only the last, partial batch of a block carries per-edge predicates.
 #pragma once
 
 #include "common.cuh"
@@ -79,19 +81,24 @@ __device__ __forceinline__ void sweep_edges(Op &op, const typename Op::Row &rc, 
         const int cnt = left < 32 ? static_cast<int>(left) : 32;
         for (int k = 0; k < cnt; k += L.ngrp * U) {
             typename Op::Frag frag[U];
-            I src[U];
+            I src[U], eid[U];
             bool ok[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int slot = k + u * L.ngrp + L.grp;
                 ok[u] = slot < cnt;
+                eid[u] = base + slot;
                 src[u] = shfl_idx(mine, slot & 31);
-                if (ok[u]) op.load(src[u], frag[u]);
             }
+            if (k + L.ngrp * U <= cnt) {  // warp-uniform: a full batch needs no per-edge predicate
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int slot = k + u * L.ngrp + L.grp;
-                op.consume(rc, st, frag[u], src[u], base + slot, ok[u]);
+                for (int u = 0; u < U; ++u) op.load(src[u], frag[u]);
+                op.template consume<true>(rc, st, frag, src, eid, ok);
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (ok[u]) op.load(src[u], frag[u]);
+                op.template consume<false>(rc, st, frag, src, eid, ok);
             }
         }
         mine = next;
