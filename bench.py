@@ -182,9 +182,11 @@ class Job:
         g, x = self.graph, self.inputs
         if self.op == "gt":
             if self.shard:
-                out = tdist.sharded_graph_transformer_aggr(self.shard, x[0], x[1], x[2], self.wl.params["scale"])
+                out = tdist.sharded_graph_transformer_aggr(self.shard, x[0], x[1], x[2], self.wl.params["scale"],
+                                                           forward_light_warps=1)
             else:
-                out = tg.graph_transformer_aggr(g, None, x[0], x[1], x[2], self.wl.params["scale"])
+                out = tg.graph_transformer_aggr(g, None, x[0], x[1], x[2], self.wl.params["scale"],
+                                                forward_light_warps=1)
             return (out,) + torch.autograd.grad(out, x, self.grad)
         if self.op == "gatv2":
             if self.shard:

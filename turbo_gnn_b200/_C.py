@@ -99,20 +99,23 @@ def _chunk_elems(dt: torch.dtype) -> int:
     return 4 if dt == torch.float32 else 8
 
 
-def _rows_ok(t: torch.Tensor) -> bool:
-    """True when `t` ([N,F] or [N,H,D]) can be read with 16-byte row accesses as is."""
+def _rows_ok(t: torch.Tensor, align: int = 16) -> bool:
+    """True when `t` ([N,F] or [N,H,D]) can be read with `align`-byte row accesses as is."""
     esz = t.element_size()
     if t.stride(-1) != 1 and t.shape[-1] > 1:
         return False
     if t.dim() == 3 and t.shape[1] > 1 and t.stride(1) != t.shape[2]:
         return False
-    if t.data_ptr() % 16 != 0:
+    if t.data_ptr() % align != 0:
         return False
-    return t.shape[0] <= 1 or (t.stride(0) * esz) % 16 == 0
+    return t.shape[0] <= 1 or (t.stride(0) * esz) % align == 0
 
 
-def _as_rows(t: torch.Tensor) -> torch.Tensor:
-    return t if _rows_ok(t) else t.contiguous()
+def _as_rows(t: torch.Tensor, align: int = 16) -> torch.Tensor:
+    if _rows_ok(t, align):
+        return t
+    t = t.contiguous()
+    return t if t.data_ptr() % align == 0 else t.clone()
 
 
 def _pad_cols(t: torch.Tensor, cols: int) -> torch.Tensor:
@@ -449,7 +452,7 @@ def _head_rows(t: torch.Tensor, d_pad: int) -> torch.Tensor:
         raise RuntimeError(f"expected [N, H, D], got {tuple(t.shape)}")
     if t.shape[2] != d_pad:
         t = F.pad(t, (0, d_pad - t.shape[2]))
-    return _as_rows(t)
+    return _as_rows(t, 32)  # the attention kernels use 256-bit accesses
 
 
 def _clamp_light(w: int) -> int:
@@ -512,7 +515,7 @@ def gatv2_forward(l, r, row_ptr, col_idx, attn_vec, negative_slope, light_nodes,
     lw, hw = _clamp_light(light_warps_per_block), _clamp_heavy(heavy_warps_per_block)
     dp = _padded_head_dim(d)
     l_in, r_in = _head_rows(l, dp), _head_rows(r, dp)
-    a_in = _pad_cols(attn_vec, dp).contiguous()
+    a_in = _as_rows(_pad_cols(attn_vec, dp), 32)
     out = torch.empty((n_rows, heads, dp), dtype=l.dtype, device=l.device)
     lse = torch.empty((n_rows, heads), dtype=torch.float32, device=l.device)
     if n_rows > 0:
@@ -547,7 +550,7 @@ def gatv2_backward_dst(grad_h, l, r, row_ptr, col_idx, attn_vec, lse, G, negativ
     n_rows, heads, d = l.shape
     dp = _padded_head_dim(d)
     l_in, r_in, g_in = _head_rows(l, dp), _head_rows(r, dp), _head_rows(grad_h, dp)
-    a_in = _pad_cols(attn_vec, dp).contiguous()
+    a_in = _as_rows(_pad_cols(attn_vec, dp), 32)
     grad_l = torch.empty((n_rows, heads, dp), dtype=l.dtype, device=l.device)
     if grad_attn_f32 is None:
         grad_attn_f32 = torch.zeros((heads, dp), dtype=torch.float32, device=l.device)
@@ -586,7 +589,7 @@ def gatv2_backward_src(grad_h, l, r, row_ptr_T, col_idx_T, attn_vec, lse, G, neg
     n_src, heads, d = r.shape
     dp = _padded_head_dim(d)
     l_in, r_in, g_in = _head_rows(l, dp), _head_rows(r, dp), _head_rows(grad_h, dp)
-    a_in = _pad_cols(attn_vec, dp).contiguous()
+    a_in = _as_rows(_pad_cols(attn_vec, dp), 32)
     grad_r = torch.empty((n_src, heads, dp), dtype=r.dtype, device=r.device)
     if n_src > 0:
         sched = _sched(row_ptr_T, light_nodes, heavy_nodes)

@@ -108,6 +108,36 @@ Geometry make_geometry(int64_t cols, int chunk_elems, int min_group_lanes) {
     return g;
 }
 
+Geometry make_attn_geometry(int64_t cols, int head_dim, int32_t dtype) {
+    const int per = dtype == TGNN_F32 ? 4 : 8;
+    const int64_t chunks = (cols + per - 1) / per;
+    const int chunks_per_head = head_dim / per > 0 ? head_dim / per : 1;
+    Geometry g;
+    g.vpl = 1;
+    while (g.vpl < 8 && g.vpl * 2 <= chunks_per_head && 32 * g.vpl < chunks) g.vpl *= 2;
+    const int64_t lanes = (chunks + g.vpl - 1) / g.vpl;
+    int lanes_per_head = chunks_per_head / g.vpl;
+    if (lanes_per_head < 1) lanes_per_head = 1;
+    if (lanes <= 32) {
+        g.G = ilog2_ceil_pow2(static_cast<int>(lanes));
+        if (g.G < lanes_per_head) g.G = lanes_per_head;
+        if (g.G > 32) g.G = 32;
+        g.slices = 1;
+    } else {
+        g.G = 32;
+        g.slices = static_cast<int>((lanes + 31) / 32);
+    }
+    return g;
+}
+
+int32_t check_attn_mat(const tgnn_mat &m, const char *name, int64_t rows, int64_t cols, int32_t dtype) {
+    TGNN_TRY(check_mat(m, name, rows, cols, dtype));
+    const size_t pitch = static_cast<size_t>(m.row_stride) * dtype_size(m.dtype);
+    TGNN_REQUIRE((reinterpret_cast<uintptr_t>(m.data) & 31u) == 0 && pitch % 32 == 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "%s: attention operands need a 32-byte aligned base address and row pitch", name);
+    return TGNN_OK;
+}
+
 }  // namespace tgnn
 
 extern "C" {

@@ -16,44 +16,28 @@ int32_t check_heads(int heads, int head_dim, int64_t cols, int32_t dtype) {
     return TGNN_OK;
 }
 
-// The group of lanes that shares an edge must hold whole heads.
-Geometry attn_geometry(int64_t cols, int head_dim, int32_t dtype) {
-    const int per = dtype == TGNN_F32 ? 4 : 8;
-    int lanes_per_head = head_dim / per;
-    if (lanes_per_head > 32) lanes_per_head = 32;
-    return make_geometry(cols, per, lanes_per_head);
-}
-
 // One warp per row: dot[v, h] = <a[v, h, :], b[v, h, :]>.
 template <typename T, int kVpl>
 __global__ void __launch_bounds__(256) head_dot_kernel(const T *__restrict__ a, int64_t lda, const T *__restrict__ b,
                                                         int64_t ldb, float *__restrict__ dot, int64_t rows, int cols,
                                                         int heads, int head_dim, int G) {
     constexpr int kPer = Elem<T>::kPerChunk;
+    constexpr int kVals = kVpl * kPer;
     Lanes L = make_lanes(G);
-    // Every lane group would do the same row; use the whole warp as one group.
-    L.G = 32;
-    L.g_lane = L.lane;
-    L.grp = 0;
-    L.ngrp = 1;
+    // Every lane group would do the same row; keep the first group only.
     const AttnMap<kVpl, kPer> map(L, cols);
-    const HeadMap<kVpl, kPer> hm(L, map, head_dim);
+    const HeadMap hm(L, map, head_dim);
     const int warps = blockDim.x >> 5;
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); row < rows;
          row += static_cast<int64_t>(gridDim.x) * warps) {
-        float xa[kVpl * kPer], xb[kVpl * kPer], pv[kVpl];
-        load_row_f32<T, kVpl>(a + row * lda, map, xa);
-        load_row_f32<T, kVpl>(b + row * ldb, map, xb);
+        float xa[kVals], xb[kVals], pv[1];
+        load_span_f32<T, kVpl>(a + row * lda, map.off, xa);
+        load_span_f32<T, kVpl>(b + row * ldb, map.off, xb);
+        pv[0] = 0.0f;
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            pv[v] = 0.0f;
-#pragma unroll
-            for (int e = 0; e < kPer; ++e) pv[v] = fmaf(xa[v * kPer + e], xb[v * kPer + e], pv[v]);
-        }
+        for (int i = 0; i < kVals; ++i) pv[0] = fmaf(xa[i], xb[i], pv[0]);
         hm.finish(pv);
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v)
-            if (hm.writer[v]) dot[row * heads + hm.head[v]] = pv[v];
+        if (hm.writer) dot[row * heads + hm.head] = pv[0];
     }
 }
 
@@ -88,13 +72,22 @@ size_t words_of(int32_t dtype, int32_t itype, int vpl) {
 }  // namespace
 
 size_t gatv2_scratch_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_chunks, int64_t cols) {
+    // The lane geometry depends on the head size, which this query does not know: take
+    // the largest state over the candidate chunk counts per lane.
     const int per = dtype == TGNN_F32 ? 4 : 8;
-    const Geometry geo = make_geometry(cols, per, 1);
-    size_t words = 0;
-    if (op == TGNN_OP_GATV2_FWD) words = words_of<Gatv2FwdOp>(dtype, itype, geo.vpl);
-    if (op == TGNN_OP_GATV2_BWD_DST) words = words_of<Gatv2BwdDstOp>(dtype, itype, geo.vpl);
-    if (op == TGNN_OP_GATV2_BWD_SRC) words = words_of<Gatv2BwdSrcOp>(dtype, itype, geo.vpl);
-    return static_cast<size_t>(num_chunks) * geo.slices * words * 32 * sizeof(uint32_t);
+    const int64_t chunks = (cols + per - 1) / per;
+    size_t worst = 0;
+    for (int vpl = 1; vpl <= 8; vpl *= 2) {
+        size_t words = 0;
+        if (op == TGNN_OP_GATV2_FWD) words = words_of<Gatv2FwdOp>(dtype, itype, vpl);
+        if (op == TGNN_OP_GATV2_BWD_DST) words = words_of<Gatv2BwdDstOp>(dtype, itype, vpl);
+        if (op == TGNN_OP_GATV2_BWD_SRC) words = words_of<Gatv2BwdSrcOp>(dtype, itype, vpl);
+        const int64_t lanes = (chunks + vpl - 1) / vpl;
+        const size_t slices = static_cast<size_t>((lanes + 31) / 32);
+        const size_t need = static_cast<size_t>(num_chunks) * slices * words * 32 * sizeof(uint32_t);
+        if (need > worst) worst = need;
+    }
+    return worst;
 }
 
 }  // namespace tgnn
@@ -104,12 +97,12 @@ using namespace tgnn;
 extern "C" int32_t tgnn_head_dot(const tgnn_head_dot_args *a) {
     TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
     TGNN_TRY(check_exec(a->exec));
-    TGNN_TRY(check_mat(a->a, "a", a->a.rows, a->a.cols, -1));
-    TGNN_TRY(check_mat(a->b, "b", a->a.rows, a->a.cols, a->a.dtype));
+    TGNN_TRY(check_attn_mat(a->a, "a", a->a.rows, a->a.cols, -1));
+    TGNN_TRY(check_attn_mat(a->b, "b", a->a.rows, a->a.cols, a->a.dtype));
     TGNN_TRY(check_heads(a->heads, a->head_dim, a->a.cols, a->a.dtype));
     TGNN_REQUIRE(a->dot != nullptr || a->a.rows == 0, TGNN_ERR_INVALID_ARGUMENT, "dot is null");
     if (a->a.rows == 0) return TGNN_OK;
-    const Geometry geo = attn_geometry(a->a.cols, a->head_dim, a->a.dtype);
+    const Geometry geo = make_attn_geometry(a->a.cols, a->head_dim, a->a.dtype);
     TGNN_REQUIRE(geo.slices == 1, TGNN_ERR_UNSUPPORTED, "rows wider than 256 chunks are not supported here");
     cudaStream_t stream = static_cast<cudaStream_t>(a->exec.stream);
     return dispatch_tiv(a->a.dtype, TGNN_I32, geo.vpl, [&](auto tt, auto, auto vt) -> int32_t {
@@ -120,7 +113,7 @@ extern "C" int32_t tgnn_head_dot(const tgnn_head_dot_args *a) {
         if (blocks > cap) blocks = cap;
         head_dot_kernel<T, kVpl><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
             static_cast<const T *>(a->a.data), a->a.row_stride, static_cast<const T *>(a->b.data), a->b.row_stride,
-            a->dot, a->a.rows, static_cast<int>(a->a.cols), a->heads, a->head_dim, 32);
+            a->dot, a->a.rows, static_cast<int>(a->a.cols), a->heads, a->head_dim, geo.G);
         TGNN_CUDA(cudaGetLastError());
         return TGNN_OK;
     });
@@ -132,15 +125,15 @@ extern "C" int32_t tgnn_gatv2_forward(const tgnn_gatv2_fwd_args *a) {
     TGNN_TRY(check_csr(a->csr));
     TGNN_TRY(check_schedule(a->sched, a->csr));
     const int64_t cols = a->l.cols;
-    TGNN_TRY(check_mat(a->l, "l", a->csr.num_rows, cols, -1));
-    TGNN_TRY(check_mat(a->r, "r", a->csr.num_cols, cols, a->l.dtype));
-    TGNN_TRY(check_mat(a->out, "out", a->csr.num_rows, cols, a->l.dtype));
+    TGNN_TRY(check_attn_mat(a->l, "l", a->csr.num_rows, cols, -1));
+    TGNN_TRY(check_attn_mat(a->r, "r", a->csr.num_cols, cols, a->l.dtype));
+    TGNN_TRY(check_attn_mat(a->out, "out", a->csr.num_rows, cols, a->l.dtype));
     TGNN_TRY(check_heads(a->heads, a->head_dim, cols, a->l.dtype));
-    TGNN_REQUIRE(a->attn != nullptr && aligned16(a->attn), TGNN_ERR_INVALID_ARGUMENT,
-                 "attention vector null or not 16-byte aligned");
+    TGNN_REQUIRE(a->attn != nullptr && (reinterpret_cast<uintptr_t>(a->attn) & 31u) == 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "attention vector null or not 32-byte aligned");
     TGNN_REQUIRE(a->lse != nullptr || a->csr.num_rows == 0, TGNN_ERR_INVALID_ARGUMENT, "lse is null");
     if (a->csr.num_rows == 0) return TGNN_OK;
-    const Geometry geo = attn_geometry(cols, a->head_dim, a->l.dtype);
+    const Geometry geo = make_attn_geometry(cols, a->head_dim, a->l.dtype);
     return dispatch_tiv(a->l.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
         using T = typename decltype(tt)::type;
         using I = typename decltype(it)::type;
@@ -159,18 +152,18 @@ extern "C" int32_t tgnn_gatv2_backward_dst(const tgnn_gatv2_bwd_dst_args *a) {
     TGNN_TRY(check_csr(a->csr));
     TGNN_TRY(check_schedule(a->sched, a->csr));
     const int64_t cols = a->l.cols;
-    TGNN_TRY(check_mat(a->l, "l", a->csr.num_rows, cols, -1));
-    TGNN_TRY(check_mat(a->r, "r", a->csr.num_cols, cols, a->l.dtype));
-    TGNN_TRY(check_mat(a->grad_out, "grad_out", a->csr.num_rows, cols, a->l.dtype));
-    TGNN_TRY(check_mat(a->grad_l, "grad_l", a->csr.num_rows, cols, a->l.dtype));
+    TGNN_TRY(check_attn_mat(a->l, "l", a->csr.num_rows, cols, -1));
+    TGNN_TRY(check_attn_mat(a->r, "r", a->csr.num_cols, cols, a->l.dtype));
+    TGNN_TRY(check_attn_mat(a->grad_out, "grad_out", a->csr.num_rows, cols, a->l.dtype));
+    TGNN_TRY(check_attn_mat(a->grad_l, "grad_l", a->csr.num_rows, cols, a->l.dtype));
     TGNN_TRY(check_heads(a->heads, a->head_dim, cols, a->l.dtype));
-    TGNN_REQUIRE(a->attn != nullptr && aligned16(a->attn), TGNN_ERR_INVALID_ARGUMENT,
-                 "attention vector null or not 16-byte aligned");
+    TGNN_REQUIRE(a->attn != nullptr && (reinterpret_cast<uintptr_t>(a->attn) & 31u) == 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "attention vector null or not 32-byte aligned");
     TGNN_REQUIRE(a->grad_attn_f32 != nullptr, TGNN_ERR_INVALID_ARGUMENT, "grad_attn_f32 is null");
     TGNN_REQUIRE((a->lse != nullptr && a->G != nullptr) || a->csr.num_rows == 0, TGNN_ERR_INVALID_ARGUMENT,
                  "lse or G is null");
     if (a->csr.num_rows == 0) return TGNN_OK;
-    const Geometry geo = attn_geometry(cols, a->head_dim, a->l.dtype);
+    const Geometry geo = make_attn_geometry(cols, a->head_dim, a->l.dtype);
     return dispatch_tiv(a->l.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
         using T = typename decltype(tt)::type;
         using I = typename decltype(it)::type;
@@ -193,17 +186,17 @@ extern "C" int32_t tgnn_gatv2_backward_src(const tgnn_gatv2_bwd_src_args *a) {
     TGNN_TRY(check_csr(a->csr_t));
     TGNN_TRY(check_schedule(a->sched, a->csr_t));
     const int64_t cols = a->r.cols;
-    TGNN_TRY(check_mat(a->r, "r", a->csr_t.num_rows, cols, -1));
-    TGNN_TRY(check_mat(a->l, "l", a->csr_t.num_cols, cols, a->r.dtype));
-    TGNN_TRY(check_mat(a->grad_out, "grad_out", a->csr_t.num_cols, cols, a->r.dtype));
-    TGNN_TRY(check_mat(a->grad_r, "grad_r", a->csr_t.num_rows, cols, a->r.dtype));
+    TGNN_TRY(check_attn_mat(a->r, "r", a->csr_t.num_rows, cols, -1));
+    TGNN_TRY(check_attn_mat(a->l, "l", a->csr_t.num_cols, cols, a->r.dtype));
+    TGNN_TRY(check_attn_mat(a->grad_out, "grad_out", a->csr_t.num_cols, cols, a->r.dtype));
+    TGNN_TRY(check_attn_mat(a->grad_r, "grad_r", a->csr_t.num_rows, cols, a->r.dtype));
     TGNN_TRY(check_heads(a->heads, a->head_dim, cols, a->r.dtype));
-    TGNN_REQUIRE(a->attn != nullptr && aligned16(a->attn), TGNN_ERR_INVALID_ARGUMENT,
-                 "attention vector null or not 16-byte aligned");
+    TGNN_REQUIRE(a->attn != nullptr && (reinterpret_cast<uintptr_t>(a->attn) & 31u) == 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "attention vector null or not 32-byte aligned");
     TGNN_REQUIRE((a->lse != nullptr && a->G != nullptr) || a->csr_t.num_cols == 0, TGNN_ERR_INVALID_ARGUMENT,
                  "lse or G is null");
     if (a->csr_t.num_rows == 0) return TGNN_OK;
-    const Geometry geo = attn_geometry(cols, a->head_dim, a->r.dtype);
+    const Geometry geo = make_attn_geometry(cols, a->head_dim, a->r.dtype);
     return dispatch_tiv(a->r.dtype, a->csr_t.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
         using T = typename decltype(tt)::type;
         using I = typename decltype(it)::type;

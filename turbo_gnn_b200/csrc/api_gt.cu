@@ -15,13 +15,6 @@ int32_t check_gt_heads(int heads, int head_dim, int64_t cols) {
     return TGNN_OK;
 }
 
-Geometry gt_geometry(int64_t cols, int head_dim, int32_t dtype) {
-    const int per = dtype == TGNN_F32 ? 4 : 8;
-    int lanes_per_head = head_dim / per;
-    if (lanes_per_head > 32) lanes_per_head = 32;
-    return make_geometry(cols, per, lanes_per_head);
-}
-
 template <typename T>
 GtParams<T> base_params(const tgnn_mat &q, const tgnn_mat &k, const tgnn_mat &v, int heads, int head_dim,
                         float scale) {
@@ -54,13 +47,21 @@ size_t words_of(int32_t dtype, int32_t itype, int vpl) {
 }  // namespace
 
 size_t gt_scratch_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_chunks, int64_t cols) {
+    // Largest state over the candidate chunk counts per lane (the head size is not known here).
     const int per = dtype == TGNN_F32 ? 4 : 8;
-    const Geometry geo = make_geometry(cols, per, 1);
-    size_t words = 0;
-    if (op == TGNN_OP_GT_FWD) words = words_of<GtFwdOp>(dtype, itype, geo.vpl);
-    if (op == TGNN_OP_GT_BWD_DST) words = words_of<GtBwdDstOp>(dtype, itype, geo.vpl);
-    if (op == TGNN_OP_GT_BWD_SRC) words = words_of<GtBwdSrcOp>(dtype, itype, geo.vpl);
-    return static_cast<size_t>(num_chunks) * geo.slices * words * 32 * sizeof(uint32_t);
+    const int64_t chunks = (cols + per - 1) / per;
+    size_t worst = 0;
+    for (int vpl = 1; vpl <= 8; vpl *= 2) {
+        size_t words = 0;
+        if (op == TGNN_OP_GT_FWD) words = words_of<GtFwdOp>(dtype, itype, vpl);
+        if (op == TGNN_OP_GT_BWD_DST) words = words_of<GtBwdDstOp>(dtype, itype, vpl);
+        if (op == TGNN_OP_GT_BWD_SRC) words = words_of<GtBwdSrcOp>(dtype, itype, vpl);
+        const int64_t lanes = (chunks + vpl - 1) / vpl;
+        const size_t slices = static_cast<size_t>((lanes + 31) / 32);
+        const size_t need = static_cast<size_t>(num_chunks) * slices * words * 32 * sizeof(uint32_t);
+        if (need > worst) worst = need;
+    }
+    return worst;
 }
 
 }  // namespace tgnn
@@ -73,14 +74,14 @@ extern "C" int32_t tgnn_gt_forward(const tgnn_gt_fwd_args *a) {
     TGNN_TRY(check_csr(a->csr));
     TGNN_TRY(check_schedule(a->sched, a->csr));
     const int64_t cols = a->q.cols;
-    TGNN_TRY(check_mat(a->q, "Q", a->csr.num_cols, cols, -1));
-    TGNN_TRY(check_mat(a->k, "K", a->csr.num_rows, cols, a->q.dtype));
-    TGNN_TRY(check_mat(a->v, "V", a->csr.num_cols, cols, a->q.dtype));
-    TGNN_TRY(check_mat(a->out, "out", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->q, "Q", a->csr.num_cols, cols, -1));
+    TGNN_TRY(check_attn_mat(a->k, "K", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->v, "V", a->csr.num_cols, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->out, "out", a->csr.num_rows, cols, a->q.dtype));
     TGNN_TRY(check_gt_heads(a->heads, a->head_dim, cols));
     TGNN_REQUIRE(a->lse != nullptr || a->csr.num_rows == 0, TGNN_ERR_INVALID_ARGUMENT, "lse is null");
     if (a->csr.num_rows == 0) return TGNN_OK;
-    const Geometry geo = gt_geometry(cols, a->head_dim, a->q.dtype);
+    const Geometry geo = make_attn_geometry(cols, a->head_dim, a->q.dtype);
     return dispatch_tiv(a->q.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
         using T = typename decltype(tt)::type;
         using I = typename decltype(it)::type;
@@ -99,16 +100,16 @@ extern "C" int32_t tgnn_gt_backward_dst(const tgnn_gt_bwd_dst_args *a) {
     TGNN_TRY(check_csr(a->csr));
     TGNN_TRY(check_schedule(a->sched, a->csr));
     const int64_t cols = a->q.cols;
-    TGNN_TRY(check_mat(a->q, "Q", a->csr.num_cols, cols, -1));
-    TGNN_TRY(check_mat(a->k, "K", a->csr.num_rows, cols, a->q.dtype));
-    TGNN_TRY(check_mat(a->v, "V", a->csr.num_cols, cols, a->q.dtype));
-    TGNN_TRY(check_mat(a->d_out, "dO", a->csr.num_rows, cols, a->q.dtype));
-    TGNN_TRY(check_mat(a->dk, "dK", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->q, "Q", a->csr.num_cols, cols, -1));
+    TGNN_TRY(check_attn_mat(a->k, "K", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->v, "V", a->csr.num_cols, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->d_out, "dO", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->dk, "dK", a->csr.num_rows, cols, a->q.dtype));
     TGNN_TRY(check_gt_heads(a->heads, a->head_dim, cols));
     TGNN_REQUIRE((a->lse != nullptr && a->delta != nullptr) || a->csr.num_rows == 0, TGNN_ERR_INVALID_ARGUMENT,
                  "lse or delta is null");
     if (a->csr.num_rows == 0) return TGNN_OK;
-    const Geometry geo = gt_geometry(cols, a->head_dim, a->q.dtype);
+    const Geometry geo = make_attn_geometry(cols, a->head_dim, a->q.dtype);
     return dispatch_tiv(a->q.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
         using T = typename decltype(tt)::type;
         using I = typename decltype(it)::type;
@@ -130,17 +131,17 @@ extern "C" int32_t tgnn_gt_backward_src(const tgnn_gt_bwd_src_args *a) {
     TGNN_TRY(check_csr(a->csr_t));
     TGNN_TRY(check_schedule(a->sched, a->csr_t));
     const int64_t cols = a->q.cols;
-    TGNN_TRY(check_mat(a->q, "Q", a->csr_t.num_rows, cols, -1));
-    TGNN_TRY(check_mat(a->v, "V", a->csr_t.num_rows, cols, a->q.dtype));
-    TGNN_TRY(check_mat(a->k, "K", a->csr_t.num_cols, cols, a->q.dtype));
-    TGNN_TRY(check_mat(a->d_out, "dO", a->csr_t.num_cols, cols, a->q.dtype));
-    TGNN_TRY(check_mat(a->dq, "dQ", a->csr_t.num_rows, cols, a->q.dtype));
-    TGNN_TRY(check_mat(a->dv, "dV", a->csr_t.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->q, "Q", a->csr_t.num_rows, cols, -1));
+    TGNN_TRY(check_attn_mat(a->v, "V", a->csr_t.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->k, "K", a->csr_t.num_cols, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->d_out, "dO", a->csr_t.num_cols, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->dq, "dQ", a->csr_t.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_attn_mat(a->dv, "dV", a->csr_t.num_rows, cols, a->q.dtype));
     TGNN_TRY(check_gt_heads(a->heads, a->head_dim, cols));
     TGNN_REQUIRE((a->lse != nullptr && a->delta != nullptr) || a->csr_t.num_cols == 0, TGNN_ERR_INVALID_ARGUMENT,
                  "lse or delta is null");
     if (a->csr_t.num_rows == 0) return TGNN_OK;
-    const Geometry geo = gt_geometry(cols, a->head_dim, a->q.dtype);
+    const Geometry geo = make_attn_geometry(cols, a->head_dim, a->q.dtype);
     return dispatch_tiv(a->q.dtype, a->csr_t.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
         using T = typename decltype(tt)::type;
         using I = typename decltype(it)::type;

@@ -117,6 +117,24 @@ __device__ __forceinline__ void st_stream16(void *p, const uint4 &v) {
                  : "memory");
 }
 
+// 32-byte (256-bit) forms of the three accesses above; sm_100 has 256-bit global
+// loads and stores.  `p` must be 32-byte aligned.
+__device__ __forceinline__ void ld_gather32(const void *p, uint64_t policy, uint4 &lo, uint4 &hi) {
+    asm volatile("ld.global.nc.L2::cache_hint.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8], %9;"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(p), "l"(policy));
+}
+__device__ __forceinline__ void ld_stream32(const void *p, uint4 &lo, uint4 &hi) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(p));
+}
+__device__ __forceinline__ void st_stream32(void *p, const uint4 &lo, const uint4 &hi) {
+    asm volatile("st.global.cs.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+                 "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                 : "memory");
+}
+
 template <typename I>
 __device__ __forceinline__ I ld_index(const I *p) {
     return __ldg(p);

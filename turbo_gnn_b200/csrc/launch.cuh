@@ -64,6 +64,11 @@ struct Geometry {
     int slices;  // grid.y
 };
 Geometry make_geometry(int64_t cols, int chunk_elems, int min_group_lanes);
+// Geometry of the attention ops: every lane owns `vpl` consecutive chunks that lie
+// inside one head (vpl <= head_dim / chunk_elems); a lane group holds whole heads.
+Geometry make_attn_geometry(int64_t cols, int head_dim, int32_t dtype);
+// check_mat plus 32-byte alignment of base and pitch: the attention ops use 256-bit accesses.
+int32_t check_attn_mat(const tgnn_mat &m, const char *name, int64_t rows, int64_t cols, int32_t dtype);
 
 template <class Op>
 size_t hub_scratch_bytes(int64_t num_chunks, int slices) {

@@ -1,16 +1,19 @@
 // Shared pieces of the fused attention ops (GATv2 and graph transformer).
 //
-// A node row is [heads * head_dim]; a warp (or a group of G lanes) covers it in
-// 16-byte chunks, lane-contiguous, so one head occupies `lanes_per_head`
-// consecutive lanes of one chunk index v (or, for head_dim > 32 chunks, all 32
-// lanes of several v).  Per-head dot products are finished with xor shuffles
-// inside that lane range; every lane of a head then holds the head's score and
-// runs the softmax bookkeeping for its own accumulators redundantly.
+// Lane mapping.  A node row is [heads * head_dim].  Each lane owns kVpl
+// CONSECUTIVE 16-byte chunks of it (kVpl * 16 contiguous bytes, fetched with
+// 256-bit loads when kVpl >= 2), and the host picks kVpl so that this span never
+// exceeds one head.  A head therefore occupies `lanes_per_head` = head_dim /
+// (elements per lane) consecutive lanes, every lane belongs to exactly one head,
+// and a per-head dot product is a per-lane partial sum followed by a
+// log2(lanes_per_head)-step xor-shuffle tree: one reduced value per edge and
+// lane, one softmax state (m, s) per lane.
 //
-// Edges are folded in batches of kUnroll: all scores of a batch are reduced by
-// one unrolled shuffle tree, the running maximum moves once per batch, and the
-// accumulators are rescaled once per batch.  Softmax runs in the base-2 domain
-// (scores are pre-multiplied by log2 e, `ex2.approx` / `lg2.approx`).
+// Edges are folded in batches of kUnroll: all dot products of a batch go through
+// one unrolled shuffle tree; the running maximum and the accumulator rescale are
+// touched only when some lane's maximum moved (warp-uniform test), which after
+// the first few edges of a row is rare.  Softmax runs in the base-2 domain
+// (scores pre-multiplied by log2 e, `ex2.approx` / `lg2.approx`).
 #pragma once
 
 #include "ops_reduce.cuh"
@@ -31,41 +34,31 @@ __device__ __forceinline__ float fast_log2(float x) {
     return y;
 }
 
-// Chunk offsets for the attention ops: chunks beyond the row are clamped to
-// offset 0 so that the edge loop needs no per-chunk predicate (their lanes
-// compute values nobody stores; a head never mixes clamped and real chunks
-// because rows end on a head boundary).  `live[v]` gates the stores.
+// Where this lane's span of the row starts.  A lane beyond the row reads
+// offset 0 instead (its results are never stored), so the edge loop carries no
+// per-lane predicate; rows end on a head boundary, so a head is all live or all dead.
 template <int kVpl, int kPer>
 struct AttnMap {
-    int off[kVpl];
-    bool live[kVpl];
+    int off;    // element offset of the first owned chunk
+    bool live;  // the span lies inside the row
     __device__ __forceinline__ AttnMap(const Lanes &L, int cols) {
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            const int o = ((L.slice * kVpl + v) * L.G + L.g_lane) * kPer;
-            live[v] = o < cols;
-            off[v] = live[v] ? o : 0;
-        }
+        const int o = (L.slice * L.G + L.g_lane) * kVpl * kPer;
+        live = o < cols;
+        off = live ? o : 0;
     }
 };
 
-// Head layout of one lane.
-template <int kVpl, int kPer>
+// Head of this lane and the shuffle span of a head.
 struct HeadMap {
-    int lanes_per_head;  // shuffle span, <= 32
-    int v_per_head;      // chunk indices v that belong to one head (1 unless head_dim > 32 chunks)
-    int head[kVpl];      // head index of chunk v
-    bool writer[kVpl];   // this lane stores the per-head scalars of chunk v's head
+    int lanes_per_head;  // 1, 2, 4, 8, 16 or 32
+    int head;            // head index of this lane
+    bool writer;         // this lane stores the per-head scalars (first lane of the head, group 0)
 
+    template <int kVpl, int kPer>
     __device__ __forceinline__ HeadMap(const Lanes &L, const AttnMap<kVpl, kPer> &map, int head_dim) {
-        const int cph = head_dim / kPer;
-        lanes_per_head = cph > 32 ? 32 : cph;
-        v_per_head = cph > 32 ? cph / 32 : 1;
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            head[v] = map.off[v] / head_dim;
-            writer[v] = map.live[v] && (map.off[v] % head_dim) == 0 && L.grp == 0;
-        }
+        lanes_per_head = head_dim / (kVpl * kPer);
+        head = map.off / head_dim;
+        writer = map.live && (map.off % head_dim) == 0 && L.grp == 0;
     }
 
     template <int kLanes, int kN>
@@ -77,26 +70,10 @@ struct HeadMap {
         }
     }
 
-    // x[j * kVpl + v]: this lane's partial dot product over chunk v (j = edge of
-    // the batch, or any other outer index).  On return every entry is the full
-    // dot product of its head, in every lane of that head.
+    // x[i]: this lane's partial dot products.  On return every x[i] is the sum over
+    // the lanes of this lane's head.
     template <int kN>
     __device__ __forceinline__ void finish(float (&x)[kN]) const {
-        if (v_per_head > 1) {
-#pragma unroll
-            for (int j = 0; j < kN / kVpl; ++j) {
-                float tot[kVpl];
-#pragma unroll
-                for (int v = 0; v < kVpl; ++v) {
-                    tot[v] = 0.0f;
-#pragma unroll
-                    for (int u = 0; u < kVpl; ++u)
-                        if (u / v_per_head == v / v_per_head) tot[v] += x[j * kVpl + u];
-                }
-#pragma unroll
-                for (int v = 0; v < kVpl; ++v) x[j * kVpl + v] = tot[v];
-            }
-        }
         switch (lanes_per_head) {  // warp-uniform
             case 32: tree<32>(x); break;
             case 16: tree<16>(x); break;
@@ -108,85 +85,66 @@ struct HeadMap {
     }
 };
 
-// Running softmax-weighted sum of gathered rows (base-2 domain): per chunk v a
-// running max m, a running denominator s and kPer numerators.
-template <int kVpl, int kPer>
+// Running softmax-weighted sum of gathered rows (base-2 domain).
+template <int kVals>
 struct SoftmaxAcc {
-    static constexpr int kVals = kVpl * kPer;
-    static constexpr int kWords = kVals + 2 * kVpl;
+    static constexpr int kWords = kVals + 2;
     float acc[kVals];
-    float m[kVpl];
-    float s[kVpl];
+    float m;
+    float s;
 
     __device__ __forceinline__ void init() {
 #pragma unroll
         for (int i = 0; i < kVals; ++i) acc[i] = 0.0f;
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            m[v] = -INFINITY;
-            s[v] = 0.0f;
-        }
+        m = -INFINITY;
+        s = 0.0f;
     }
-    // Fold a batch of kU edges into chunk v.  sc[j]: base-2 score of edge j for
-    // chunk v's head (-inf for an absent edge when !kAll); x[j]: the value chunk.
-    // Returns nothing; with !kAll a batch without any edge leaves the state as is.
+    // Fold a batch of kU edges.  sc[j]: base-2 score of edge j for this lane's head
+    // (-inf for an absent edge when !kAll); x[j]: the lane's span of the value row.
     template <int kU, bool kAll>
-    __device__ __forceinline__ void push(int v, const float (&sc)[kU], const float (&x)[kU][kPer]) {
-        float m_new = m[v];
+    __device__ __forceinline__ void push(const float (&sc)[kU], const float (&x)[kU][kVals]) {
+        float m_new = m;
 #pragma unroll
         for (int j = 0; j < kU; ++j) m_new = fmaxf(m_new, sc[j]);
-        if (!kAll && m_new == -INFINITY) return;
-        const float corr = fast_exp2(m[v] - m_new);  // 0 for the first batch (m = -inf)
-        float p[kU];
-        float psum = 0.0f;
+        if (__any_sync(kFull, m_new > m)) {  // rare once a row is under way
+            // 0 when m was -inf; a lane group that still has no edge (m_new = -inf) is left alone
+            const float corr = m_new == -INFINITY ? 1.0f : fast_exp2(m - m_new);
+            s *= corr;
+#pragma unroll
+            for (int i = 0; i < kVals; ++i) acc[i] *= corr;
+            m = m_new;
+        }
+        if (!kAll && m == -INFINITY) return;  // this lane group has seen no edge yet
 #pragma unroll
         for (int j = 0; j < kU; ++j) {
-            p[j] = fast_exp2(sc[j] - m_new);
-            psum += p[j];
-        }
-        s[v] = fmaf(s[v], corr, psum);
+            const float p = fast_exp2(sc[j] - m);
+            s += p;
 #pragma unroll
-        for (int e = 0; e < kPer; ++e) {
-            float a = acc[v * kPer + e] * corr;
-#pragma unroll
-            for (int j = 0; j < kU; ++j) a = fmaf(p[j], x[j][e], a);
-            acc[v * kPer + e] = a;
+            for (int i = 0; i < kVals; ++i) acc[i] = fmaf(p, x[j][i], acc[i]);
         }
-        m[v] = m_new;
     }
     __device__ __forceinline__ void merge(const SoftmaxAcc &o) {
+        const float m_new = fmaxf(m, o.m);
+        const float c1 = m == -INFINITY ? 0.0f : fast_exp2(m - m_new);
+        const float c2 = o.m == -INFINITY ? 0.0f : fast_exp2(o.m - m_new);
+        s = s * c1 + o.s * c2;
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            const float m_new = fmaxf(m[v], o.m[v]);
-            const float c1 = m[v] == -INFINITY ? 0.0f : fast_exp2(m[v] - m_new);
-            const float c2 = o.m[v] == -INFINITY ? 0.0f : fast_exp2(o.m[v] - m_new);
-            s[v] = s[v] * c1 + o.s[v] * c2;
-#pragma unroll
-            for (int e = 0; e < kPer; ++e) acc[v * kPer + e] = acc[v * kPer + e] * c1 + o.acc[v * kPer + e] * c2;
-            m[v] = m_new;
-        }
+        for (int i = 0; i < kVals; ++i) acc[i] = acc[i] * c1 + o.acc[i] * c2;
+        m = m_new;
     }
-    // Natural-log log-sum-exp of chunk v's head; -inf for a row without edges.
-    __device__ __forceinline__ float lse(int v) const {
-        return s[v] > 0.0f ? (m[v] + fast_log2(s[v])) * kLn2 : -INFINITY;
-    }
+    // Natural-log log-sum-exp; -inf for a row without edges.
+    __device__ __forceinline__ float lse() const { return s > 0.0f ? (m + fast_log2(s)) * kLn2 : -INFINITY; }
     __device__ __forceinline__ void to_words(uint32_t *w) const {
 #pragma unroll
         for (int i = 0; i < kVals; ++i) w[i] = __float_as_uint(acc[i]);
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            w[kVals + v] = __float_as_uint(m[v]);
-            w[kVals + kVpl + v] = __float_as_uint(s[v]);
-        }
+        w[kVals] = __float_as_uint(m);
+        w[kVals + 1] = __float_as_uint(s);
     }
     __device__ __forceinline__ void from_words(const uint32_t *w) {
 #pragma unroll
         for (int i = 0; i < kVals; ++i) acc[i] = __uint_as_float(w[i]);
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            m[v] = __uint_as_float(w[kVals + v]);
-            s[v] = __uint_as_float(w[kVals + kVpl + v]);
-        }
+        m = __uint_as_float(w[kVals]);
+        s = __uint_as_float(w[kVals + 1]);
     }
 };
 
@@ -212,27 +170,57 @@ struct SumAcc {
     }
 };
 
-// Row-local operand: the chunks of one row as floats (clamped chunks read offset 0).
-template <typename T, int kVpl>
-__device__ __forceinline__ void load_row_f32(const T *row, const AttnMap<kVpl, Elem<T>::kPerChunk> &map, float *dst) {
-    constexpr int kPer = Elem<T>::kPerChunk;
+// A lane's span of one row, raw (kVpl chunks).
+template <int kVpl>
+struct Span {
+    uint4 c[kVpl];
+    __device__ __forceinline__ void clear() {
 #pragma unroll
-    for (int v = 0; v < kVpl; ++v) Elem<T>::unpack(ld_stream16(row + map.off[v]), dst + v * kPer);
+        for (int v = 0; v < kVpl; ++v) c[v] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    template <typename T>
+    __device__ __forceinline__ void to_f32(float *dst) const {
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) Elem<T>::unpack(c[v], dst + v * Elem<T>::kPerChunk);
+    }
+};
+
+// Gather this lane's span of row `row` (kept in L2 in preference to streamed data).
+template <typename T, int kVpl>
+__device__ __forceinline__ void gather_span(const T *row, int off, uint64_t keep, Span<kVpl> &s) {
+    constexpr int kPer = Elem<T>::kPerChunk;
+    if (kVpl == 1) {
+        s.c[0] = ld_gather16(row + off, keep);
+    } else {
+#pragma unroll
+        for (int v = 0; v < kVpl; v += 2) ld_gather32(row + off + v * kPer, keep, s.c[v], s.c[v + 1 < kVpl ? v + 1 : v]);
+    }
+}
+
+// Row-local operand (read once): this lane's span as floats.
+template <typename T, int kVpl>
+__device__ __forceinline__ void load_span_f32(const T *row, int off, float *dst) {
+    constexpr int kPer = Elem<T>::kPerChunk;
+    Span<kVpl> s;
+    if (kVpl == 1) {
+        s.c[0] = ld_stream16(row + off);
+    } else {
+#pragma unroll
+        for (int v = 0; v < kVpl; v += 2) ld_stream32(row + off + v * kPer, s.c[v], s.c[v + 1 < kVpl ? v + 1 : v]);
+    }
+    s.template to_f32<T>(dst);
 }
 
 template <typename T, int kVpl>
-__device__ __forceinline__ void store_row_f32(T *row, const AttnMap<kVpl, Elem<T>::kPerChunk> &map, const float *src) {
+__device__ __forceinline__ void store_span_f32(T *row, int off, const float *src) {
     constexpr int kPer = Elem<T>::kPerChunk;
+    if (kVpl == 1) {
+        st_stream16(row + off, Elem<T>::pack(src));
+    } else {
 #pragma unroll
-    for (int v = 0; v < kVpl; ++v)
-        if (map.live[v]) st_stream16(row + map.off[v], Elem<T>::pack(src + v * kPer));
-}
-
-template <typename T, int kVpl>
-__device__ __forceinline__ void gather_row(const T *row, const AttnMap<kVpl, Elem<T>::kPerChunk> &map, uint64_t keep,
-                                           uint4 *raw) {
-#pragma unroll
-    for (int v = 0; v < kVpl; ++v) raw[v] = ld_gather16(row + map.off[v], keep);
+        for (int v = 0; v < kVpl; v += 2)
+            st_stream32(row + off + v * kPer, Elem<T>::pack(src + v * kPer), Elem<T>::pack(src + (v + 1) * kPer));
+    }
 }
 
 // Empty hooks for ops that carry nothing across rows.

@@ -36,102 +36,95 @@ struct GtParams {
     float scale;
 };
 
-template <int kVpl>
-__device__ __forceinline__ void clear_chunks(uint4 (&raw)[kVpl]) {
-#pragma unroll
-    for (int v = 0; v < kVpl; ++v) raw[v] = make_uint4(0u, 0u, 0u, 0u);
-}
-
-// ---- forward ----------------------------------------------------------------------
+// Lane geometry shared by the three ops.
 template <typename T, typename I, int kVpl>
-struct GtFwdOp {
+struct GtBase {
     using index_t = I;
     using Params = GtParams<T>;
     static constexpr int kPer = Elem<T>::kPerChunk;
     static constexpr int kVals = kVpl * kPer;
-    using Acc = SoftmaxAcc<kVpl, kPer>;
+
+    const Params &p;
+    const Lanes &L;
+    AttnMap<kVpl, kPer> map;
+    HeadMap hm;
+    uint64_t keep;
+
+    __device__ __forceinline__ GtBase(const Params &p_, const Lanes &L_)
+        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {}
+};
+
+// ---- forward ----------------------------------------------------------------------
+template <typename T, typename I, int kVpl>
+struct GtFwdOp : GtBase<T, I, kVpl> {
+    using B = GtBase<T, I, kVpl>;
+    using typename B::index_t;
+    using typename B::Params;
+    using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p;
+    using Acc = SoftmaxAcc<kVals>;
     static constexpr int kWords = Acc::kWords;
     static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
     static constexpr int kCarryWords = 0;
 
     struct Row {
-        float k[kVals];  // key row times scale * log2(e)
+        float k[kVals];  // key span times scale * log2(e)
     };
     using State = Acc;
     using Carry = NoCarry;
     struct Frag {
-        uint4 rawq[kVpl];
-        uint4 rawv[kVpl];
+        Span<kVpl> q;
+        Span<kVpl> v;
     };
 
-    const Params &p;
-    const Lanes &L;
-    AttnMap<kVpl, kPer> map;
-    HeadMap<kVpl, kPer> hm;
-    uint64_t keep;
-
-    __device__ __forceinline__ GtFwdOp(const Params &p_, const Lanes &L_)
-        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {}
+    __device__ __forceinline__ GtFwdOp(const Params &p_, const Lanes &L_) : B(p_, L_) {}
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
-        load_row_f32<T, kVpl>(p.k + static_cast<int64_t>(row) * p.ldk, map, rc.k);
+        load_span_f32<T, kVpl>(p.k + static_cast<int64_t>(row) * p.ldk, map.off, rc.k);
         const float f = p.scale * kLog2e;
 #pragma unroll
         for (int i = 0; i < kVals; ++i) rc.k[i] *= f;
     }
     __device__ __forceinline__ void init(State &s) { s.init(); }
     __device__ __forceinline__ void load(I src, Frag &f) {
-        gather_row<T, kVpl>(p.q + static_cast<int64_t>(src) * p.ldq, map, keep, f.rawq);
-        gather_row<T, kVpl>(p.v + static_cast<int64_t>(src) * p.ldv, map, keep, f.rawv);
+        gather_span<T, kVpl>(p.q + static_cast<int64_t>(src) * p.ldq, map.off, keep, f.q);
+        gather_span<T, kVpl>(p.v + static_cast<int64_t>(src) * p.ldv, map.off, keep, f.v);
     }
     template <bool kAll>
     __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
                                             const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
-        float sc[kUnroll * kVpl];
+        float sc[kUnroll];
+        float x[kUnroll][kVals];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             if (!kAll && !ok[u]) {
-                clear_chunks<kVpl>(f[u].rawq);
-                clear_chunks<kVpl>(f[u].rawv);
+                f[u].q.clear();
+                f[u].v.clear();
             }
+            f[u].q.template to_f32<T>(x[u]);
+            float acc = 0.0f;
 #pragma unroll
-            for (int v = 0; v < kVpl; ++v) {
-                float x[kPer];
-                Elem<T>::unpack(f[u].rawq[v], x);
-                float acc = 0.0f;
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) acc = fmaf(x[e], rc.k[v * kPer + e], acc);
-                sc[u * kVpl + v] = acc;
-            }
+            for (int i = 0; i < kVals; ++i) acc = fmaf(x[u][i], rc.k[i], acc);
+            sc[u] = acc;
+            f[u].v.template to_f32<T>(x[u]);
         }
         hm.finish(sc);
+        if (!kAll) {
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            float s2[kUnroll];
-            float x[kUnroll][kPer];
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                s2[u] = (kAll || ok[u]) ? sc[u * kVpl + v] : -INFINITY;
-                Elem<T>::unpack(f[u].rawv[v], x[u]);
-            }
-            s.template push<kUnroll, kAll>(v, s2, x);
+            for (int u = 0; u < kUnroll; ++u)
+                if (!ok[u]) sc[u] = -INFINITY;
         }
+        s.template push<kUnroll, kAll>(sc, x);
     }
     __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
     __device__ __forceinline__ void to_words(const State &s, uint32_t *w) { s.to_words(w); }
     __device__ __forceinline__ void from_words(State &s, const uint32_t *w) { s.from_words(w); }
     __device__ __forceinline__ void row_end(I row, const Row &, State &s, I) {
-        if (L.grp != 0) return;
-        T *orow = p.out0 + static_cast<int64_t>(row) * p.ldo0;
+        if (L.grp != 0 || !map.live) return;
+        const float inv = s.s > 0.0f ? 1.0f / s.s : 0.0f;
+        float x[kVals];
 #pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            if (!map.live[v]) continue;
-            const float inv = s.s[v] > 0.0f ? 1.0f / s.s[v] : 0.0f;
-            float x[kPer];
-#pragma unroll
-            for (int e = 0; e < kPer; ++e) x[e] = s.acc[v * kPer + e] * inv;
-            st_stream16(orow + map.off[v], Elem<T>::pack(x));
-            if (hm.writer[v]) p.lse_out[static_cast<int64_t>(row) * p.heads + hm.head[v]] = s.lse(v);
-        }
+        for (int i = 0; i < kVals; ++i) x[i] = s.acc[i] * inv;
+        store_span_f32<T, kVpl>(p.out0 + static_cast<int64_t>(row) * p.ldo0, map.off, x);
+        if (hm.writer) p.lse_out[static_cast<int64_t>(row) * p.heads + hm.head] = s.lse();
     }
     __device__ __forceinline__ void flush_row(State &) {}
     __device__ __forceinline__ void carry_init(Carry &) {}
@@ -141,11 +134,11 @@ struct GtFwdOp {
 
 // ---- backward, destination side: dk over the forward CSR ----------------------------------
 template <typename T, typename I, int kVpl>
-struct GtBwdDstOp {
-    using index_t = I;
-    using Params = GtParams<T>;
-    static constexpr int kPer = Elem<T>::kPerChunk;
-    static constexpr int kVals = kVpl * kPer;
+struct GtBwdDstOp : GtBase<T, I, kVpl> {
+    using B = GtBase<T, I, kVpl>;
+    using typename B::index_t;
+    using typename B::Params;
+    using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p;
     static constexpr int kWords = kVals;
     static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
     static constexpr int kCarryWords = 0;
@@ -153,88 +146,71 @@ struct GtBwdDstOp {
     struct Row {
         float k[kVals];  // times scale * log2(e)
         float dO[kVals];
-        float lse2[kVpl];
-        float delta[kVpl];
+        float lse2;
+        float delta;
     };
     using State = SumAcc<kVals>;
     using Carry = NoCarry;
     struct Frag {
-        uint4 rawq[kVpl];
-        uint4 rawv[kVpl];
+        Span<kVpl> q;
+        Span<kVpl> v;
     };
 
-    const Params &p;
-    const Lanes &L;
-    AttnMap<kVpl, kPer> map;
-    HeadMap<kVpl, kPer> hm;
-    uint64_t keep;
-
-    __device__ __forceinline__ GtBwdDstOp(const Params &p_, const Lanes &L_)
-        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {}
+    __device__ __forceinline__ GtBwdDstOp(const Params &p_, const Lanes &L_) : B(p_, L_) {}
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
-        load_row_f32<T, kVpl>(p.k + static_cast<int64_t>(row) * p.ldk, map, rc.k);
-        load_row_f32<T, kVpl>(p.d_out + static_cast<int64_t>(row) * p.ldd, map, rc.dO);
+        load_span_f32<T, kVpl>(p.k + static_cast<int64_t>(row) * p.ldk, map.off, rc.k);
+        load_span_f32<T, kVpl>(p.d_out + static_cast<int64_t>(row) * p.ldd, map.off, rc.dO);
         const float f = p.scale * kLog2e;
 #pragma unroll
         for (int i = 0; i < kVals; ++i) rc.k[i] *= f;
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            const int64_t at = static_cast<int64_t>(row) * p.heads + hm.head[v];
-            rc.lse2[v] = __ldg(p.lse + at) * kLog2e;
-            rc.delta[v] = __ldg(p.delta + at);
-        }
+        const int64_t at = static_cast<int64_t>(row) * p.heads + hm.head;
+        rc.lse2 = __ldg(p.lse + at) * kLog2e;
+        rc.delta = __ldg(p.delta + at);
     }
     __device__ __forceinline__ void init(State &s) { s.init(); }
     __device__ __forceinline__ void load(I src, Frag &f) {
-        gather_row<T, kVpl>(p.q + static_cast<int64_t>(src) * p.ldq, map, keep, f.rawq);
-        gather_row<T, kVpl>(p.v + static_cast<int64_t>(src) * p.ldv, map, keep, f.rawv);
+        gather_span<T, kVpl>(p.q + static_cast<int64_t>(src) * p.ldq, map.off, keep, f.q);
+        gather_span<T, kVpl>(p.v + static_cast<int64_t>(src) * p.ldv, map.off, keep, f.v);
     }
     template <bool kAll>
     __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
                                             const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
-        float d[2 * kUnroll * kVpl];
+        float d[2 * kUnroll];
+        float xq[kUnroll][kVals];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             if (!kAll && !ok[u]) {
-                clear_chunks<kVpl>(f[u].rawq);
-                clear_chunks<kVpl>(f[u].rawv);
+                f[u].q.clear();
+                f[u].v.clear();
             }
+            float xv[kVals];
+            f[u].q.template to_f32<T>(xq[u]);
+            f[u].v.template to_f32<T>(xv);
+            float ps = 0.0f, pd = 0.0f;
 #pragma unroll
-            for (int v = 0; v < kVpl; ++v) {
-                float xq[kPer], xv[kPer];
-                Elem<T>::unpack(f[u].rawq[v], xq);
-                Elem<T>::unpack(f[u].rawv[v], xv);
-                float ps = 0.0f, pd = 0.0f;
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) {
-                    ps = fmaf(xq[e], rc.k[v * kPer + e], ps);
-                    pd = fmaf(xv[e], rc.dO[v * kPer + e], pd);
-                }
-                d[u * kVpl + v] = ps;
-                d[(kUnroll + u) * kVpl + v] = pd;
+            for (int i = 0; i < kVals; ++i) {
+                ps = fmaf(xq[u][i], rc.k[i], ps);
+                pd = fmaf(xv[i], rc.dO[i], pd);
             }
+            d[u] = ps;
+            d[kUnroll + u] = pd;
         }
         hm.finish(d);
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
+            float alpha = fast_exp2(d[u] - rc.lse2);
+            if (!kAll && !ok[u]) alpha = 0.0f;
+            const float ds = alpha * (d[kUnroll + u] - rc.delta) * p.scale;
 #pragma unroll
-            for (int v = 0; v < kVpl; ++v) {
-                float alpha = fast_exp2(d[u * kVpl + v] - rc.lse2[v]);
-                if (!kAll && !ok[u]) alpha = 0.0f;
-                const float ds = alpha * (d[(kUnroll + u) * kVpl + v] - rc.delta[v]) * p.scale;
-                float xq[kPer];
-                Elem<T>::unpack(f[u].rawq[v], xq);
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) s.a[v * kPer + e] = fmaf(ds, xq[e], s.a[v * kPer + e]);
-            }
+            for (int i = 0; i < kVals; ++i) s.a[i] = fmaf(ds, xq[u][i], s.a[i]);
         }
     }
     __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
     __device__ __forceinline__ void to_words(const State &s, uint32_t *w) { s.to_words(w); }
     __device__ __forceinline__ void from_words(State &s, const uint32_t *w) { s.from_words(w); }
     __device__ __forceinline__ void row_end(I row, const Row &, State &s, I) {
-        if (L.grp != 0) return;
-        store_row_f32<T, kVpl>(p.out0 + static_cast<int64_t>(row) * p.ldo0, map, s.a);
+        if (L.grp != 0 || !map.live) return;
+        store_span_f32<T, kVpl>(p.out0 + static_cast<int64_t>(row) * p.ldo0, map.off, s.a);
     }
     __device__ __forceinline__ void flush_row(State &) {}
     __device__ __forceinline__ void carry_init(Carry &) {}
@@ -244,11 +220,11 @@ struct GtBwdDstOp {
 
 // ---- backward, source side: dq and dv over the transposed CSR --------------------------------
 template <typename T, typename I, int kVpl>
-struct GtBwdSrcOp {
-    using index_t = I;
-    using Params = GtParams<T>;
-    static constexpr int kPer = Elem<T>::kPerChunk;
-    static constexpr int kVals = kVpl * kPer;
+struct GtBwdSrcOp : GtBase<T, I, kVpl> {
+    using B = GtBase<T, I, kVpl>;
+    using typename B::index_t;
+    using typename B::Params;
+    using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p;
     static constexpr int kWords = 2 * kVals;  // dq | dv
     static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
     static constexpr int kCarryWords = 0;
@@ -260,82 +236,61 @@ struct GtBwdSrcOp {
     using State = SumAcc<2 * kVals>;
     using Carry = NoCarry;
     struct Frag {
-        uint4 rawk[kVpl];
-        uint4 rawd[kVpl];
-        float lse[kVpl];
-        float delta[kVpl];
+        Span<kVpl> k;
+        Span<kVpl> d;
+        float lse;
+        float delta;
     };
 
-    const Params &p;
-    const Lanes &L;
-    AttnMap<kVpl, kPer> map;
-    HeadMap<kVpl, kPer> hm;
-    uint64_t keep;
-
-    __device__ __forceinline__ GtBwdSrcOp(const Params &p_, const Lanes &L_)
-        : p(p_), L(L_), map(L_, p_.cols), hm(L_, map, p_.head_dim), keep(make_keep_policy()) {}
+    __device__ __forceinline__ GtBwdSrcOp(const Params &p_, const Lanes &L_) : B(p_, L_) {}
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
-        load_row_f32<T, kVpl>(p.q + static_cast<int64_t>(row) * p.ldq, map, rc.q);
-        load_row_f32<T, kVpl>(p.v + static_cast<int64_t>(row) * p.ldv, map, rc.v);
+        load_span_f32<T, kVpl>(p.q + static_cast<int64_t>(row) * p.ldq, map.off, rc.q);
+        load_span_f32<T, kVpl>(p.v + static_cast<int64_t>(row) * p.ldv, map.off, rc.v);
         const float f = p.scale * kLog2e;
 #pragma unroll
         for (int i = 0; i < kVals; ++i) rc.q[i] *= f;
     }
     __device__ __forceinline__ void init(State &s) { s.init(); }
     __device__ __forceinline__ void load(I dst, Frag &f) {
-        gather_row<T, kVpl>(p.k + static_cast<int64_t>(dst) * p.ldk, map, keep, f.rawk);
-        gather_row<T, kVpl>(p.d_out + static_cast<int64_t>(dst) * p.ldd, map, keep, f.rawd);
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v) {
-            const int64_t at = static_cast<int64_t>(dst) * p.heads + hm.head[v];
-            f.lse[v] = __ldg(p.lse + at);
-            f.delta[v] = __ldg(p.delta + at);
-        }
+        gather_span<T, kVpl>(p.k + static_cast<int64_t>(dst) * p.ldk, map.off, keep, f.k);
+        gather_span<T, kVpl>(p.d_out + static_cast<int64_t>(dst) * p.ldd, map.off, keep, f.d);
+        const int64_t at = static_cast<int64_t>(dst) * p.heads + hm.head;
+        f.lse = __ldg(p.lse + at);
+        f.delta = __ldg(p.delta + at);
     }
     template <bool kAll>
     __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
                                             const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
-        float d[2 * kUnroll * kVpl];
+        float d[2 * kUnroll];
+        float xk[kUnroll][kVals], xd[kUnroll][kVals];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             if (!kAll && !ok[u]) {
-                clear_chunks<kVpl>(f[u].rawk);
-                clear_chunks<kVpl>(f[u].rawd);
-#pragma unroll
-                for (int v = 0; v < kVpl; ++v) f[u].lse[v] = f[u].delta[v] = 0.0f;
+                f[u].k.clear();
+                f[u].d.clear();
+                f[u].lse = f[u].delta = 0.0f;
             }
+            f[u].k.template to_f32<T>(xk[u]);
+            f[u].d.template to_f32<T>(xd[u]);
+            float ps = 0.0f, pd = 0.0f;
 #pragma unroll
-            for (int v = 0; v < kVpl; ++v) {
-                float xk[kPer], xd[kPer];
-                Elem<T>::unpack(f[u].rawk[v], xk);
-                Elem<T>::unpack(f[u].rawd[v], xd);
-                float ps = 0.0f, pd = 0.0f;
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) {
-                    ps = fmaf(xk[e], rc.q[v * kPer + e], ps);
-                    pd = fmaf(xd[e], rc.v[v * kPer + e], pd);
-                }
-                d[u * kVpl + v] = ps;
-                d[(kUnroll + u) * kVpl + v] = pd;
+            for (int i = 0; i < kVals; ++i) {
+                ps = fmaf(xk[u][i], rc.q[i], ps);
+                pd = fmaf(xd[u][i], rc.v[i], pd);
             }
+            d[u] = ps;
+            d[kUnroll + u] = pd;
         }
         hm.finish(d);
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
+            float alpha = fast_exp2(fmaf(-f[u].lse, kLog2e, d[u]));
+            if (!kAll && !ok[u]) alpha = 0.0f;
+            const float ds = alpha * (d[kUnroll + u] - f[u].delta) * p.scale;
 #pragma unroll
-            for (int v = 0; v < kVpl; ++v) {
-                float alpha = fast_exp2(fmaf(-f[u].lse[v], kLog2e, d[u * kVpl + v]));
-                if (!kAll && !ok[u]) alpha = 0.0f;
-                const float ds = alpha * (d[(kUnroll + u) * kVpl + v] - f[u].delta[v]) * p.scale;
-                float xk[kPer], xd[kPer];
-                Elem<T>::unpack(f[u].rawk[v], xk);
-                Elem<T>::unpack(f[u].rawd[v], xd);
-#pragma unroll
-                for (int e = 0; e < kPer; ++e) {
-                    const int i = v * kPer + e;
-                    s.a[i] = fmaf(ds, xk[e], s.a[i]);
-                    s.a[kVals + i] = fmaf(alpha, xd[e], s.a[kVals + i]);
-                }
+            for (int i = 0; i < kVals; ++i) {
+                s.a[i] = fmaf(ds, xk[u][i], s.a[i]);
+                s.a[kVals + i] = fmaf(alpha, xd[u][i], s.a[kVals + i]);
             }
         }
     }
@@ -343,9 +298,9 @@ struct GtBwdSrcOp {
     __device__ __forceinline__ void to_words(const State &s, uint32_t *w) { s.to_words(w); }
     __device__ __forceinline__ void from_words(State &s, const uint32_t *w) { s.from_words(w); }
     __device__ __forceinline__ void row_end(I row, const Row &, State &s, I) {
-        if (L.grp != 0) return;
-        store_row_f32<T, kVpl>(p.out0 + static_cast<int64_t>(row) * p.ldo0, map, s.a);
-        store_row_f32<T, kVpl>(p.out1 + static_cast<int64_t>(row) * p.ldo1, map, s.a + kVals);
+        if (L.grp != 0 || !map.live) return;
+        store_span_f32<T, kVpl>(p.out0 + static_cast<int64_t>(row) * p.ldo0, map.off, s.a);
+        store_span_f32<T, kVpl>(p.out1 + static_cast<int64_t>(row) * p.ldo1, map.off, s.a + kVals);
     }
     __device__ __forceinline__ void flush_row(State &) {}
     __device__ __forceinline__ void carry_init(Carry &) {}
