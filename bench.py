@@ -400,6 +400,7 @@ def main_ours(args):
     _abi.trace.reset(True)
     timed_steps(job.step, args.steps, world)
     per_call = _abi.trace.mean_ms()
+    calls_per_step = {k: len(v) / args.steps for k, v in _abi.trace.events.items()}
     launches = _abi.trace.kernel_launches
     _abi.trace.reset(False)
     model = job.entry_bytes()
@@ -414,7 +415,7 @@ def main_ours(args):
                 traffic = rec["bytes_per_edge"] * job.local_edges
     except (OSError, ValueError):
         pass
-    step_bytes = sum(model[k] for k in per_call if k in model)
+    step_bytes = sum(model[k] * calls_per_step[k] for k in per_call if k in model)
     roofline = {
         "bound": "hbm",
         "kernel": top,

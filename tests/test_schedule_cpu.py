@@ -44,7 +44,26 @@ def test_cache_hits_on_same_tensors_and_misses_on_new_ones():
     assert c is not a
     r = g.repartition(forward_huge_degree_threshold_quantile=0.5)
     d = _schedule.get_schedule(r.forward_indptr, r.forward_light_nodes, r.forward_heavy_nodes)
-    assert d is not a and d.light.numel() != a.light.numel()
+    assert d is not a
+
+
+def test_automatic_thresholds_follow_the_work_per_warp_slot():
+    chunk, hub_min, cta_min = _schedule.auto_thresholds(114_000_000, torch.device("cpu"))
+    fair = 114_000_000 // (148 * 16)
+    assert cta_min == fair // 2 and hub_min == 4 * fair and chunk % 32 == 0 and 1024 <= chunk <= 32768
+    chunk, hub_min, cta_min = _schedule.auto_thresholds(10_000, torch.device("cpu"))
+    assert (chunk, hub_min, cta_min) == (1024, 2048, 64)
+    # small graph: every heavy-list row is shorter than cta_min_degree and runs warp-per-row
+    n = 300
+    g = make_graph(random_edges(n, 3000, 5, hubs=2, hub_degree=200), n, torch.int32, quantile=0.9, device="cpu")
+    s = _schedule.split_tiers(g.forward_indptr, g.forward_light_nodes, g.forward_heavy_nodes)
+    assert s.heavy.numel() == 2 and s.hub.numel() == 0 and s.light.numel() == n - 2  # only the two long rows get CTAs
+    # explicit thresholds restore the plain light / heavy / hub split
+    s = _schedule.split_tiers(g.forward_indptr, g.forward_light_nodes, g.forward_heavy_nodes, 64, 100)
+    assert s.light.numel() == g.forward_light_nodes.numel() and s.hub.numel() == 2
+    s = _schedule.split_tiers(g.forward_indptr, g.forward_light_nodes, g.forward_heavy_nodes, 64, 100,
+                              cta_min_degree=50)
+    assert s.light.numel() > g.forward_light_nodes.numel() and s.hub.numel() == 2
 
 
 def test_bad_chunk_size_raises_runtime_error():

@@ -32,37 +32,37 @@ _HEAD_DIMS = (16, 32, 64, 128, 256)
 # tier, 2 and 4 give each light row a small CTA of its own.
 _LIGHT_CTA_WARPS = 4
 
-# Tunables of the hub tier that the reference signatures have no slot for.
-# `configure_hub_tier` changes them process-wide (the autotuner does).
+# Tier thresholds that the reference signatures have no slot for.  ``None`` = derive from
+# the graph (turbo_gnn_b200._schedule.auto_thresholds).  `configure_hub_tier` changes them
+# process-wide; the autotuner and the tests use the `hub_tier` context manager.
 _hub_cfg = {
     "chunk_edges": _schedule.DEFAULT_CHUNK_EDGES,
     "hub_min_degree": _schedule.DEFAULT_HUB_MIN_DEGREE,
+    "cta_min_degree": _schedule.DEFAULT_CTA_MIN_DEGREE,
     "sort_by_degree": True,
 }
 
 
-def configure_hub_tier(chunk_edges: int | None = None, hub_min_degree: int | None = None,
-                       sort_by_degree: bool | None = None) -> dict:
-    """Set the hub-tier parameters used by later calls; returns the previous values."""
+def configure_hub_tier(**values) -> dict:
+    """Set tier parameters (``chunk_edges``, ``hub_min_degree``, ``cta_min_degree``, ``sort_by_degree``)
+    for later calls; a value of ``None`` selects the automatic threshold.  Returns the previous values."""
+    unknown = set(values) - set(_hub_cfg)
+    if unknown:
+        raise TypeError(f"unknown tier parameter(s): {sorted(unknown)}")
     old = dict(_hub_cfg)
-    if chunk_edges is not None:
-        _hub_cfg["chunk_edges"] = int(chunk_edges)
-    if hub_min_degree is not None:
-        _hub_cfg["hub_min_degree"] = int(hub_min_degree)
-    if sort_by_degree is not None:
-        _hub_cfg["sort_by_degree"] = bool(sort_by_degree)
+    _hub_cfg.update(values)
     return old
 
 
 class hub_tier:
-    """Context manager: run the enclosed calls with the given hub-tier parameters."""
+    """Context manager: run the enclosed calls with the given tier parameters."""
 
-    def __init__(self, chunk_edges=None, hub_min_degree=None, sort_by_degree=None):
-        self._new = (chunk_edges, hub_min_degree, sort_by_degree)
+    def __init__(self, **values):
+        self._new = values
         self._old = None
 
     def __enter__(self):
-        self._old = configure_hub_tier(*self._new)
+        self._old = configure_hub_tier(**self._new)
         return self
 
     def __exit__(self, *exc):
@@ -74,9 +74,10 @@ def current_hub_config() -> dict:
     return dict(_hub_cfg)
 
 
-def _sched(indptr, light, heavy):
-    return _schedule.get_schedule(indptr, light, heavy, _hub_cfg["chunk_edges"], _hub_cfg["hub_min_degree"],
-                                  _hub_cfg["sort_by_degree"])
+def _sched(indptr, light, heavy, chunk_edges="cfg", slots=_schedule.ATTENTION_WARP_SLOTS):
+    chunk = _hub_cfg["chunk_edges"] if chunk_edges == "cfg" else chunk_edges
+    return _schedule.get_schedule(indptr, light, heavy, chunk, _hub_cfg["hub_min_degree"],
+                                  _hub_cfg["sort_by_degree"], _hub_cfg["cta_min_degree"], slots)
 
 
 def _check_index_family(indptr, *others):
@@ -180,10 +181,10 @@ def reduction_aggr_forward_partitioned(
     if minmax and want_arg:
         arg = torch.empty((n_rows, cols), dtype=edge_ptr.dtype, device=X.device)
     if n_rows > 0 and feat > 0:
-        sched = _schedule.get_schedule(
-            edge_ptr, light_nodes, heavy_nodes, int(edges_per_block_heavy_nodes) * 16
-            if not use_2d_kernel else _hub_cfg["chunk_edges"], _hub_cfg["hub_min_degree"], _hub_cfg["sort_by_degree"]
-        )
+        # the reference's edges-per-block (32..2048) scales to this library's hub chunk (x16)
+        sched = _sched(edge_ptr, light_nodes, heavy_nodes,
+                       "cfg" if use_2d_kernel else int(edges_per_block_heavy_nodes) * 16,
+                       _schedule.REDUCE_WARP_SLOTS)
         op = _abi.OP_REDUCE_MINMAX if minmax else _abi.OP_WEIGHTED_SUM
         ws, ws_bytes = _scratch(op, sched, x_in, edge_ptr.dtype, cols)
         heavy_warps = int(tiles_y) if use_2d_kernel else 8
@@ -359,7 +360,8 @@ def csr_SPMM_normalized(
         if g.sched is None:
             light, heavy = _bucket(indptr)
             g.sched = _schedule.split_tiers(indptr, light, heavy, _hub_cfg["chunk_edges"],
-                                            _hub_cfg["hub_min_degree"], _hub_cfg["sort_by_degree"])
+                                            _hub_cfg["hub_min_degree"], _hub_cfg["sort_by_degree"],
+                                            _hub_cfg["cta_min_degree"], _schedule.REDUCE_WARP_SLOTS)
         run_ptr, run_idx, sched, out_rows, src_rows = indptr, indices, g.sched, n_rows, g.num_cols
         w = edge_weights.float().contiguous() if has_w else None
         rs, cs = row_scale, col_scale
@@ -370,7 +372,8 @@ def csr_SPMM_normalized(
         if g.t_sched is None:
             light, heavy = _bucket(t_ptr)
             g.t_sched = _schedule.split_tiers(t_ptr, light, heavy, _hub_cfg["chunk_edges"],
-                                              _hub_cfg["hub_min_degree"], _hub_cfg["sort_by_degree"])
+                                              _hub_cfg["hub_min_degree"], _hub_cfg["sort_by_degree"],
+                                              _hub_cfg["cta_min_degree"], _schedule.REDUCE_WARP_SLOTS)
         run_ptr, run_idx, sched, out_rows, src_rows = t_ptr, t_idx, g.t_sched, g.num_cols, n_rows
         w = edge_weights.float()[perm].contiguous() if has_w else None
         rs, cs = col_scale, row_scale  # roles swap under transposition
@@ -797,7 +800,7 @@ def spmm_rows(indptr, indices, x, light_nodes, heavy_nodes, row_scale=None, col_
     x_in = _as_rows(_pad_cols(x, cols))
     out = torch.empty((n_rows, cols), dtype=x.dtype, device=x.device)
     if n_rows > 0:
-        sched = _sched(indptr, light_nodes, heavy_nodes)
+        sched = _sched(indptr, light_nodes, heavy_nodes, slots=_schedule.REDUCE_WARP_SLOTS)
         ws, ws_bytes = _scratch(_abi.OP_WEIGHTED_SUM, sched, x_in, indptr.dtype, cols)
         args = _abi.SpmmArgs(
             exec=_abi.exec_of(x_in),

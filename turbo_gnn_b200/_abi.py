@@ -12,6 +12,7 @@ There is no fallback: if the shared library has not been built, every op raises.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 from pathlib import Path
 
@@ -290,7 +291,9 @@ _lib_lock = threading.Lock()
 
 
 def library_path() -> Path:
-    return Path(__file__).resolve().parent / LIB_NAME
+    """The in-tree library, or the file named by TURBO_GNN_B200_LIB (e.g. a build with other flags)."""
+    override = os.environ.get("TURBO_GNN_B200_LIB")
+    return Path(override) if override else Path(__file__).resolve().parent / LIB_NAME
 
 
 def load_library() -> C.CDLL:

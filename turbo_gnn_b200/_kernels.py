@@ -28,8 +28,8 @@ def _quantile_axis(side: str) -> list[TunableParam]:
 class _HubTunables:
     """Hub-tier attributes shared by the attention kernels; applied around each execution."""
 
-    hub_chunk_edges = 2048
-    hub_min_degree = 4096
+    hub_chunk_edges = None  # None: derived from the graph
+    hub_min_degree = None
 
     def _hub(self):
         return _C.hub_tier(chunk_edges=self.hub_chunk_edges, hub_min_degree=self.hub_min_degree)
@@ -37,8 +37,8 @@ class _HubTunables:
     @staticmethod
     def _hub_axes() -> list[TunableParam]:
         return [
-            TunableParam("hub_chunk_edges", [1024, 4096], default=2048),
-            TunableParam("hub_min_degree", [2048, 16384], default=4096),
+            TunableParam("hub_chunk_edges", [None, 2048], default=None),
+            TunableParam("hub_min_degree", [None, 4096], default=None),
         ]
 
 

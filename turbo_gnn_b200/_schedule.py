@@ -3,11 +3,25 @@
 The reference schedules two buckets (``turbo_gnn/graph.py:11-36``) and edge-splits
 only the heavy rows of its min/max kernel over a ``num_heavy x ceil(max_degree / EPB)``
 grid in which most CTAs exit at once (``csrc/reduction/reduction_aggr.cu:157-159,558``).
-Here the heavy list is divided once more: rows of at least ``hub_min_degree``
-edges become hub rows, cut into exact chunks of ``chunk_edges`` edges (one CTA
-each, merged by a second pass); the rest stay one CTA per row; light rows get
-one warp each.  The chunk tables are small device tensors built with torch
-ops and cached per (indptr, light, heavy, parameters).
+Here the light/heavy lists of the graph are the CANDIDATES for the tiers and the
+row's degree decides:
+
+* light tier (one warp per row): every light row, and every heavy-list row shorter
+  than ``cta_min_degree``;
+* heavy tier (one CTA per row): heavy-list rows of ``cta_min_degree`` .. ``hub_min_degree`` edges;
+* hub tier: heavy-list rows of at least ``hub_min_degree`` edges, cut into exact
+  chunks of ``chunk_edges`` edges (one CTA each, merged by a second pass).
+
+Left at ``None`` the three numbers follow from the work per warp slot,
+``fair = edges / (SMs * 16)``: one warp can take a row of up to about half a fair
+share without becoming the tail of the launch (rows are issued longest first), a
+CTA one of a few fair shares, anything longer is split.  Measured on B200: on a
+114 M-edge graph (fair = 48 k edges, longest row 21 k) warp-per-row for ALL rows
+beats any use of the CTA / hub tiers by 10-15 %, while a 2.5 M-edge graph
+(fair = 1 k) needs CTAs for its 1-2 k-edge rows.
+
+The chunk tables are small device tensors built with torch ops and cached per
+(indptr, light, heavy, parameters).
 """
 
 from __future__ import annotations
@@ -20,10 +34,15 @@ import torch
 
 from . import _abi
 
-# Launch defaults of the hub tier; both are tunable per call.
-DEFAULT_CHUNK_EDGES = 2048
-DEFAULT_HUB_MIN_DEGREE = 4096
+# None = derive from the graph (see module docstring); integers force a value.
+DEFAULT_CHUNK_EDGES = None
+DEFAULT_HUB_MIN_DEGREE = None
+DEFAULT_CTA_MIN_DEGREE = None
 
+# Resident warps per SM the kernels typically reach: the register-heavy attention ops
+# run at about 16, the reductions / SpMM at about 64.
+ATTENTION_WARP_SLOTS = 16
+REDUCE_WARP_SLOTS = 64
 _CACHE_SLOTS = 128
 
 
@@ -67,37 +86,66 @@ def _signed(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+def _sm_count(device: torch.device) -> int:
+    if device.type == "cuda":
+        return torch.cuda.get_device_properties(device).multi_processor_count
+    return 148
+
+
+def auto_thresholds(num_edges: int, device: torch.device,
+                    slots_per_sm: int = ATTENTION_WARP_SLOTS) -> tuple[int, int, int]:
+    """``(chunk_edges, hub_min_degree, cta_min_degree)`` derived from the work per warp slot."""
+    fair = max(num_edges // (_sm_count(device) * slots_per_sm), 1)
+    cta_min = max(64, fair // 2)
+    hub_min = max(2048, 4 * fair)
+    chunk = min(max(fair // 2, 1024), 32768) // 32 * 32
+    return chunk, hub_min, cta_min
+
+
 def split_tiers(
     indptr: torch.Tensor,
     light: torch.Tensor,
     heavy: torch.Tensor,
-    chunk_edges: int = DEFAULT_CHUNK_EDGES,
-    hub_min_degree: int = DEFAULT_HUB_MIN_DEGREE,
+    chunk_edges: int | None = DEFAULT_CHUNK_EDGES,
+    hub_min_degree: int | None = DEFAULT_HUB_MIN_DEGREE,
     sort_by_degree: bool = True,
+    cta_min_degree: int | None = DEFAULT_CTA_MIN_DEGREE,
+    slots_per_sm: int = ATTENTION_WARP_SLOTS,
 ) -> TierSchedule:
-    """Build the schedule (uncached).  Works on any device; used as is by the CPU tests."""
+    """Build the schedule (uncached).  Works on any device; used as is by the CPU tests.
+
+    An explicit ``hub_min_degree`` without ``cta_min_degree`` keeps every other heavy-list row in
+    the CTA tier (``cta_min_degree = 0``), i.e. the plain light / heavy / hub split.
+    """
+    ptr = _signed(indptr)
+    dev = indptr.device
+    num_edges = int(ptr[-1].item()) - int(ptr[0].item()) if ptr.numel() > 1 else 0
+    auto_chunk, auto_hub, auto_cta = auto_thresholds(num_edges, dev, slots_per_sm)
+    if cta_min_degree is None:
+        cta_min_degree = auto_cta if hub_min_degree is None else 0
+    if hub_min_degree is None:
+        hub_min_degree = auto_hub
+    if chunk_edges is None:
+        chunk_edges = auto_chunk
     if chunk_edges < 32 or chunk_edges % 32 != 0 or chunk_edges > 65536:
         raise RuntimeError(f"Wrong int value: chunk_edges={chunk_edges} must be a multiple of 32 in [32, 65536]")
-    ptr = _signed(indptr)
     light_s, heavy_s = _signed(light), _signed(heavy)
-    dev = indptr.device
 
     def degrees(rows):
         r = rows.long()
         return (ptr[r + 1] - ptr[r]).long()
 
-    if sort_by_degree and light_s.numel() > 1:
-        # Longest rows first: warps of a CTA get rows of similar length and the
-        # long rows do not end up in the tail of the grid.
-        order = torch.argsort(degrees(light_s), descending=True, stable=True)
-        light_s = light_s[order]
     if heavy_s.numel() > 0:
         deg = degrees(heavy_s)
         is_hub = deg >= max(int(hub_min_degree), 1)
+        is_cta = (~is_hub) & (deg >= int(cta_min_degree))
+        demoted = heavy_s[~(is_hub | is_cta)]
+        if demoted.numel() > 0:
+            light_s = torch.cat([light_s, demoted])
         hub = heavy_s[is_hub]
-        rest = heavy_s[~is_hub]
+        rest = heavy_s[is_cta]
         if sort_by_degree and rest.numel() > 1:
-            rest = rest[torch.argsort(deg[~is_hub], descending=True, stable=True)]
+            rest = rest[torch.argsort(deg[is_cta], descending=True, stable=True)]
         hub_deg = deg[is_hub]
         per_row = (hub_deg + (chunk_edges - 1)) // chunk_edges
         part_ptr = torch.zeros(hub.numel() + 1, dtype=torch.int64, device=dev)
@@ -112,6 +160,11 @@ def split_tiers(
         part_ptr = torch.zeros(1, dtype=torch.int64, device=dev)
         chunk_hub = torch.zeros(0, dtype=torch.int64, device=dev)
         num_chunks = 0
+    if sort_by_degree and light_s.numel() > 1:
+        # Longest rows first: warps of a CTA get rows of similar length and the
+        # long rows do not end up in the tail of the grid.
+        order = torch.argsort(degrees(light_s), descending=True, stable=True)
+        light_s = light_s[order]
     return TierSchedule(
         light=light_s.contiguous(),
         heavy=rest.contiguous(),
@@ -130,8 +183,10 @@ class _ScheduleCache:
         self._slots = slots
         self._items: OrderedDict[tuple, tuple] = OrderedDict()
 
-    def get(self, indptr, light, heavy, chunk_edges, hub_min_degree, sort_by_degree) -> TierSchedule:
-        key = (id(indptr), id(light), id(heavy), int(chunk_edges), int(hub_min_degree), bool(sort_by_degree))
+    def get(self, indptr, light, heavy, chunk_edges, hub_min_degree, sort_by_degree, cta_min_degree,
+            slots_per_sm) -> TierSchedule:
+        key = (id(indptr), id(light), id(heavy), chunk_edges, hub_min_degree, bool(sort_by_degree), cta_min_degree,
+               slots_per_sm)
         hit = self._items.get(key)
         if hit is not None:
             refs, sched = hit
@@ -139,7 +194,8 @@ class _ScheduleCache:
                 self._items.move_to_end(key)
                 return sched
             del self._items[key]
-        sched = split_tiers(indptr, light, heavy, chunk_edges, hub_min_degree, sort_by_degree)
+        sched = split_tiers(indptr, light, heavy, chunk_edges, hub_min_degree, sort_by_degree, cta_min_degree,
+                            slots_per_sm)
         self._items[key] = ((weakref.ref(indptr), weakref.ref(light), weakref.ref(heavy)), sched)
         while len(self._items) > self._slots:
             self._items.popitem(last=False)
@@ -156,12 +212,15 @@ def get_schedule(
     indptr: torch.Tensor,
     light: torch.Tensor,
     heavy: torch.Tensor,
-    chunk_edges: int = DEFAULT_CHUNK_EDGES,
-    hub_min_degree: int = DEFAULT_HUB_MIN_DEGREE,
+    chunk_edges: int | None = DEFAULT_CHUNK_EDGES,
+    hub_min_degree: int | None = DEFAULT_HUB_MIN_DEGREE,
     sort_by_degree: bool = True,
+    cta_min_degree: int | None = DEFAULT_CTA_MIN_DEGREE,
+    slots_per_sm: int = ATTENTION_WARP_SLOTS,
 ) -> TierSchedule:
     """Cached :func:`split_tiers`."""
-    return _cache.get(indptr, light, heavy, chunk_edges, hub_min_degree, sort_by_degree)
+    return _cache.get(indptr, light, heavy, chunk_edges, hub_min_degree, sort_by_degree, cta_min_degree,
+                      slots_per_sm)
 
 
 def clear_schedule_cache() -> None:

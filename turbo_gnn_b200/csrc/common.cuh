@@ -8,6 +8,17 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// Build-time tunables of the attention kernels (override with -D to explore).
+//   TGNN_LIGHT_MIN_BLOCKS(vpl): minimum resident 256-thread CTAs per SM the warp-per-row kernel
+//                               is compiled for (caps registers per thread at 65536 / (256 * n)).
+//   TGNN_ATTN_UNROLL(vpl):      edges gathered per batch by the backward ops and the GT forward.
+#ifndef TGNN_LIGHT_MIN_BLOCKS
+#define TGNN_LIGHT_MIN_BLOCKS(vpl) ((vpl) >= 4 ? 2 : 1)
+#endif
+#ifndef TGNN_ATTN_UNROLL
+#define TGNN_ATTN_UNROLL(vpl) ((vpl) >= 4 ? 1 : 2)
+#endif
+
 namespace tgnn {
 
 constexpr int kWarp = 32;

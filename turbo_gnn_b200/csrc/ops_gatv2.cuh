@@ -73,6 +73,7 @@ struct Gatv2FwdOp : Gatv2Base<T, I, kVpl> {
     static constexpr int kWords = Acc::kWords;
     static constexpr int kUnroll = kVpl >= 4 ? 2 : 4;
     static constexpr int kCarryWords = 0;
+    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
 
     struct Row {
         float l[kVals];
@@ -140,8 +141,9 @@ struct Gatv2BwdDstOp : Gatv2Base<T, I, kVpl> {
     using typename B::Params;
     using B::a; using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p; using B::slope_m1;
     static constexpr int kWords = 2 * kVals;  // grad_l | grad_a
-    static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
+    static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = kVals;
+    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
 
     struct Row {
         float l[kVals];
@@ -250,8 +252,9 @@ struct Gatv2BwdSrcOp : Gatv2Base<T, I, kVpl> {
     using typename B::Params;
     using B::a; using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p; using B::slope_m1;
     static constexpr int kWords = kVals;
-    static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
+    static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
+    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
 
     struct Row {
         float r[kVals];

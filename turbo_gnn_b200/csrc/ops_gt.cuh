@@ -63,8 +63,9 @@ struct GtFwdOp : GtBase<T, I, kVpl> {
     using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p;
     using Acc = SoftmaxAcc<kVals>;
     static constexpr int kWords = Acc::kWords;
-    static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
+    static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
+    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
 
     struct Row {
         float k[kVals];  // key span times scale * log2(e)
@@ -140,8 +141,9 @@ struct GtBwdDstOp : GtBase<T, I, kVpl> {
     using typename B::Params;
     using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p;
     static constexpr int kWords = kVals;
-    static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
+    static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
+    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
 
     struct Row {
         float k[kVals];  // times scale * log2(e)
@@ -226,8 +228,9 @@ struct GtBwdSrcOp : GtBase<T, I, kVpl> {
     using typename B::Params;
     using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p;
     static constexpr int kWords = 2 * kVals;  // dq | dv
-    static constexpr int kUnroll = kVpl >= 4 ? 1 : 2;
+    static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
+    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
 
     struct Row {
         float q[kVals];  // times scale * log2(e)

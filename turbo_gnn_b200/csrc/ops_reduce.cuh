@@ -48,6 +48,7 @@ struct MinMaxOp {
     static constexpr int kWords = kVals * (1 + kIdxWords);
     static constexpr int kUnroll = (kVpl >= 4) ? 2 : 4;
     static constexpr int kCarryWords = 0;
+    static constexpr int kLightMinBlocks = 1;
 
     struct Row {};
     struct Carry {};
@@ -193,6 +194,7 @@ struct WeightedSumOp {
     static constexpr int kWords = kVals;
     static constexpr int kUnroll = (kVpl >= 4) ? 2 : 4;
     static constexpr int kCarryWords = 0;
+    static constexpr int kLightMinBlocks = 1;
 
     struct Row {};
     struct Carry {};
