@@ -103,16 +103,27 @@ def shard_graph(graph: AdjacencyForwardBackwardWithNodeBuckets, rank: int, world
 def gather_rows(local: torch.Tensor, shard: GraphShard, group=None, async_op: bool = False):
     """All-gather a row-sharded tensor into the padded ``[world * max_rows, ...]`` layout.
 
-    Returns the gathered tensor (and the work handle when ``async_op``).  With ``world == 1`` the
-    result is the zero-padded input and no collective runs.
+    Returns the gathered tensor (and the work handle when ``async_op``).  Rows past a rank's own
+    count are padding that no column id refers to; they are left uninitialised.  On NCCL only the
+    real rows travel (one grouped collective with per-rank sizes); other backends (gloo, for the
+    CPU tests) pad every shard to ``max_rows`` and use the equal-sized collective.  With
+    ``world == 1`` no collective runs.
     """
     tail = tuple(local.shape[1:])
-    staged = torch.zeros((shard.max_rows,) + tail, dtype=local.dtype, device=local.device)
-    staged[: local.shape[0]].copy_(local)
-    if shard.world == 1:
-        return (staged, None) if async_op else staged
     full = torch.empty((shard.world * shard.max_rows,) + tail, dtype=local.dtype, device=local.device)
-    work = dist.all_gather_into_tensor(full, staged, group=group, async_op=async_op)
+    mine = full[shard.rank * shard.max_rows: shard.rank * shard.max_rows + local.shape[0]]
+    if shard.world == 1:
+        mine.copy_(local)
+        return (full, None) if async_op else full
+    counts = [shard.bounds[p + 1] - shard.bounds[p] for p in range(shard.world)]
+    uneven = len(set(counts)) > 1 or counts[0] != shard.max_rows
+    if uneven and dist.get_backend(group) == "nccl":
+        outs = [full[p * shard.max_rows: p * shard.max_rows + counts[p]] for p in range(shard.world)]
+        work = dist.all_gather(outs, local.contiguous(), group=group, async_op=async_op)
+    else:
+        staged = torch.zeros((shard.max_rows,) + tail, dtype=local.dtype, device=local.device)
+        staged[: local.shape[0]].copy_(local)
+        work = dist.all_gather_into_tensor(full, staged, group=group, async_op=async_op)
     return (full, work) if async_op else full
 
 
