@@ -13,8 +13,8 @@ What a pass gathers FROM (source features in forward, destination-side tensors i
 source-side backward) is all-gathered into a local buffer first, one collective per pass;
 kernels then run unchanged on local memory.  Ranges have unequal lengths, so the gathered
 buffer is laid out ``[world, max_rows, F]`` (each rank's rows padded to the longest range) and
-the column ids of the shards are remapped once to that layout; this keeps the collective a
-single equal-sized ``all_gather_into_tensor``.
+the column ids of the shards are remapped once to that layout.  On NCCL only the real rows
+travel (one grouped all-gather with per-rank sizes); padding rows are never read.
 """
 
 from __future__ import annotations
