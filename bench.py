@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the aggregation hot path: aggregated edges/s (forward + backward) on N B200s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0..cfg3] [--shrink f]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg0..cfg4] [--shrink f]
     python bench.py --impl reference ...      # the CPU scatter path on the host cores
 
 A step is one forward + backward pass of the workload's op over the whole (or, with N > 1, the
@@ -24,7 +24,7 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-WORKLOADS = {"cfg0": 0, "cfg1": 1, "cfg2": 2, "cfg3": 3}
+WORKLOADS = {"cfg0": 0, "cfg1": 1, "cfg2": 2, "cfg3": 3, "cfg4": 4}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -167,8 +167,15 @@ class Job:
         elif self.op == "reduce":
             self.inputs = [pick(t["x"])]
             self.grad = None
+        elif self.op == "gatv2_model":
+            from turbo_gnn_b200.layers import TwoLayerGATv2
+
+            self.inputs = [pick(t["features"])]
+            self.model = TwoLayerGATv2(in_dim=100, hidden_heads=4, hidden_dim=64, num_classes=47, seed=4).to(dev)
+            g_up = torch.Generator(device=dev).manual_seed(1004)
+            self.grad = pick(torch.randn(wl.num_nodes, 47, generator=g_up, device=dev))
         for x in self.inputs:
-            x.requires_grad_(self.op != "reduce")
+            x.requires_grad_(self.op not in ("reduce", "gatv2_model"))
         if self.shard is not None:
             del wl.tensors, wl.graph  # the full graph is not needed after sharding
             self.wl.edge_index = None
@@ -200,24 +207,40 @@ class Job:
             else:
                 out = tg.spmm_aggr(x[0], g.forward_indptr, g.forward_indices, "none", -1, 256)
             return (out,) + torch.autograd.grad(out, x, self.grad)
+        if self.op == "gatv2_model":  # cfg4: two projection + aggregation layers, parameter gradients
+            out = self.model(x[0], self.shard if self.shard else g)
+            params = list(self.model.parameters())
+            grads = torch.autograd.grad(out, params, self.grad)
+            if self.shard:
+                import torch.distributed as dist
+
+                flat = torch.cat([gr.reshape(-1) for gr in grads])
+                dist.all_reduce(flat)  # replicated parameters: sum the per-shard gradients
+            return (out,)
         outs = []
         for red in ("min", "max", "sum", "mean"):  # cfg0: forward only, four reductions
             outs.append(tg.reduction_aggr(g, x[0], warps_per_block=4, reduce=red))
         return tuple(outs)
 
-    # ---- byte model (algorithmic bytes of one call of each library entry point, this rank) ----
+    # ---- byte model: algorithmic bytes per STEP of each library entry point, this rank ----
     def entry_bytes(self):
         E, R = self.local_edges, self.local_rows
         i = self.graph.forward_indptr.element_size()
         x0 = self.inputs[0]
         s = x0.element_size()
-        if self.op in ("gt", "gatv2"):
-            H = x0.shape[1]
-            F = x0.shape[1] * x0.shape[2]
-        else:
-            H, F = 1, x0.shape[1]
-        Fs = F * s
+
+        def gatv2(H, D):
+            Fs = H * D * s
+            return {
+                "tgnn_gatv2_forward": E * (Fs + i) + R * (2 * Fs + 4 * H),
+                "tgnn_gatv2_backward_dst": E * (Fs + i) + R * (3 * Fs + 8 * H),
+                "tgnn_gatv2_backward_src": E * (2 * Fs + i + 8 * H) + R * (2 * Fs),
+                "tgnn_head_dot": R * (2 * Fs + 4 * H),
+            }
+
         if self.op == "gt":
+            H = x0.shape[1]
+            Fs = H * x0.shape[2] * s
             return {
                 "tgnn_gt_forward": E * (2 * Fs + i) + R * (2 * Fs + 4 * H),
                 "tgnn_gt_backward_dst": E * (2 * Fs + i) + R * (3 * Fs + 8 * H),
@@ -225,15 +248,14 @@ class Job:
                 "tgnn_head_dot": R * (2 * Fs + 4 * H),
             }
         if self.op == "gatv2":
-            return {
-                "tgnn_gatv2_forward": E * (Fs + i) + R * (2 * Fs + 4 * H),
-                "tgnn_gatv2_backward_dst": E * (Fs + i) + R * (3 * Fs + 8 * H),
-                "tgnn_gatv2_backward_src": E * (2 * Fs + i + 8 * H) + R * (2 * Fs),
-                "tgnn_head_dot": R * (2 * Fs + 4 * H),
-            }
+            return gatv2(x0.shape[1], x0.shape[2])
+        if self.op == "gatv2_model":
+            l1, l2 = gatv2(4, 64), gatv2(1, 47)
+            return {k: l1[k] + l2[k] for k in l1}
+        Fs = x0.shape[1] * s
         if self.op == "spmm":
-            return {"tgnn_spmm": E * (Fs + i) + R * (Fs + i)}
-        return {"tgnn_segment_reduce_forward": E * (Fs + i) + R * (Fs + i)}
+            return {"tgnn_spmm": 2 * (E * (Fs + i) + R * (Fs + i))}  # forward + transposed backward
+        return {"tgnn_segment_reduce_forward": 4 * (E * (Fs + i) + R * (Fs + i))}  # min, max, sum, mean
 
 
 def timed_steps(fn, steps, world):
@@ -270,6 +292,14 @@ def cpu_sample(job_cfg: int, shrink: float, sample_edges: int):
     # The graph is generated where that is fast (the GPU when there is one); only the sample and
     # the feature tensors come to the host.
     where = "cuda" if torch.cuda.is_available() else "cpu"
+    if job_cfg == 4:
+        # A two-layer model needs every node's hidden state: the sample is a whole graph of the
+        # same generator, shrunk to about `sample_edges` edges.
+        wl = synthetic.make_workload(4, device=where, shrink=min(shrink, sample_edges / 1.2e8))
+        ei = wl.edge_index.long().cpu()
+        wl.tensors = {k: v.cpu() for k, v in wl.tensors.items()}
+        wl.graph, wl.edge_index = None, None
+        return wl, ei, wl.num_nodes, ei.shape[1]
     wl = synthetic.make_workload(job_cfg, device=where, shrink=shrink)
     g = wl.graph
     ptr = g.forward_indptr.long().cpu()
@@ -314,6 +344,19 @@ def cpu_step_fn(wl, ei, rows):
             out = O.spmm(x, ei, n, "none")
             return torch.autograd.grad(out, (x,), grad)
 
+    elif wl.op == "gatv2_model":
+        from turbo_gnn_b200.layers import TwoLayerGATv2
+
+        model = TwoLayerGATv2(in_dim=100, hidden_heads=4, hidden_dim=64, num_classes=47, seed=4)
+        params = [model.conv1.left_right_projection.weight, model.conv1.attn_weights,
+                  model.conv2.left_right_projection.weight, model.conv2.attn_weights]
+        x = t["features"]
+        grad = torch.randn(n, 47, generator=torch.Generator().manual_seed(1004))
+
+        def fn():
+            out = O.two_layer_gatv2(x, *params, ei, n, 0.2)
+            return torch.autograd.grad(out, params, grad)
+
     else:
         x = t["x"]
 
@@ -340,7 +383,9 @@ def run_cpu(args, steps, warmup):
         "unit": "edges/s",
         "cores": cores,
         "kind": "port",
-        "sample": f"first {rows} destination rows ({e} edges) of {wl.name}, torch scatter ops, fwd+bwd",
+        "sample": (f"{wl.name} shrunk to {rows} nodes / {e} edges, torch Linear + scatter ops, fwd+bwd"
+                   if wl.op == "gatv2_model" else
+                   f"first {rows} destination rows ({e} edges) of {wl.name}, torch scatter ops, fwd+bwd"),
         "ms_per_step": dt * 1e3,
     }
 
@@ -404,18 +449,19 @@ def main_ours(args):
     launches = _abi.trace.kernel_launches
     _abi.trace.reset(False)
     model = job.entry_bytes()
-    top = max((k for k in per_call if k in model), key=lambda k: per_call[k])
+    per_step = {k: per_call[k] * calls_per_step[k] for k in per_call}  # ms of each entry point per step
+    top = max((k for k in per_step if k in model), key=lambda k: per_step[k])
     peak, peak_kind = measured_hbm_peak()
-    achieved = model[top] / (per_call[top] * 1e-3) / 1e9
+    achieved = model[top] / (per_step[top] * 1e-3) / 1e9
     traffic = None
     try:
         with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as fh:
             rec = json.load(fh).get(f"{args.workload}:{top}")
             if rec and args.shrink == 1.0 and world == 1:
-                traffic = rec["bytes_per_edge"] * job.local_edges
+                traffic = rec["bytes_per_edge"] * job.local_edges * calls_per_step[top]
     except (OSError, ValueError):
         pass
-    step_bytes = sum(model[k] * calls_per_step[k] for k in per_call if k in model)
+    step_bytes = sum(model[k] for k in per_call if k in model)
     roofline = {
         "bound": "hbm",
         "kernel": top,
@@ -426,6 +472,7 @@ def main_ours(args):
         "frac": achieved / peak,
         "traffic": traffic,
         "ms_per_call": per_call,
+        "calls_per_step": calls_per_step,
         "step_algorithmic_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
     }
 

@@ -143,3 +143,23 @@ def attention_lse(score: torch.Tensor, dst: torch.Tensor, num_nodes: int) -> tor
     safe_top = torch.where(top.isinf(), torch.zeros_like(top), top)
     denom = torch.zeros_like(top).scatter_add_(0, idx, torch.exp(score - safe_top[dst]))
     return torch.where(denom > 0, safe_top + torch.log(denom), torch.full_like(top, float("-inf")))
+
+
+def two_layer_gatv2(x: torch.Tensor, w1: torch.Tensor, a1: torch.Tensor, w2: torch.Tensor, a2: torch.Tensor,
+                    edge_index: torch.Tensor, num_nodes: int, negative_slope: float = 0.2) -> torch.Tensor:
+    """Two GATv2 layers with an ELU between them.
+
+    Each layer is the data flow of the reference's GATv2 layer without its output projection
+    (``src/backends/torch_native_backend/conv.py``: one bias-free Linear whose output splits into
+    the destination-side and source-side halves, then the edge-softmax aggregation).  ``w`` is the
+    ``[2 * H * D, in]`` Linear weight and ``a`` the ``[H, D]`` attention vector of a layer.
+    """
+    h = x
+    for layer, (w, a) in enumerate(((w1, a1), (w2, a2))):
+        heads, d = a.shape
+        left, right = (h @ w.t()).split(heads * d, -1)
+        h = gatv2_aggregate(left.view(-1, heads, d), right.view(-1, heads, d), a, edge_index, num_nodes,
+                            negative_slope).reshape(num_nodes, heads * d)
+        if layer == 0:
+            h = F.elu(h)
+    return h

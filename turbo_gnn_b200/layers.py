@@ -1,0 +1,121 @@
+"""Layer wrappers: dense projection + fused aggregation, the immediate callers of the hot path.
+
+Mirrors the ``nn.Module`` wrappers of the reference's ``src/backends/cuda_backend/conv.py``
+(``_CudaSimpleAggrConv`` 20-41, ``_CUDAGATv2Conv`` 44-94, ``_CudaGraphTransformerConv`` 97-140):
+same parameter names (``left_right_projection``, ``attn_weights``, ``_outer_proj``, ``qkv_proj``)
+and the same forward data flow, so state dicts are interchangeable.  The projections are plain
+``nn.Linear`` (library GEMM); the two halves of the fused left/right projection are handed to the
+kernels as strided views, without a copy.  Every layer also accepts a
+:class:`turbo_gnn_b200.dist.GraphShard` in place of the graph and then works on the rows this
+rank owns.
+
+``TwoLayerGATv2`` is the two-layer model of the fifth benchmark workload: Linear -> 4 heads x 64,
+GATv2 aggregation, ELU, Linear -> 1 head x 47, GATv2 aggregation.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Literal
+
+import torch
+from torch import nn
+
+from . import dist as tdist
+from .graph import AdjacencyForwardBackwardWithNodeBuckets
+from .ops import gatv2_aggr, graph_transformer_aggr, reduction_aggr
+
+
+def _is_shard(graph) -> bool:
+    return isinstance(graph, tdist.GraphShard)
+
+
+class SimpleAggrConv(nn.Module):
+    """min / max / sum / mean aggregation as a layer (reference: ``_CudaSimpleAggrConv``)."""
+
+    def __init__(self, aggr_type: Literal["min", "max", "sum", "mean"] = "min", **kwargs: Any) -> None:
+        super().__init__()
+        self.aggr_type = aggr_type
+
+    def forward(self, x: torch.Tensor, graph: AdjacencyForwardBackwardWithNodeBuckets, **kwargs: Any) -> torch.Tensor:
+        return reduction_aggr(graph, x, reduce=self.aggr_type)
+
+
+class GATv2Conv(nn.Module):
+    """GATv2 layer: one Linear produces the destination-side and source-side projections at once.
+
+    ``head_dim`` defaults to ``feature_dim`` (the reference's layer); ``out_proj=False`` drops the
+    output projection and returns the ``[N, heads * head_dim]`` aggregation.  ``train_attention``
+    lets gradients reach ``attn_weights`` (the reference passes ``attn_weights.data``).
+    """
+
+    def __init__(self, feature_dim: int, bias: bool = False, heads: int = 1, negative_slope: float = 0.2,
+                 head_dim: int | None = None, out_proj: bool = True, train_attention: bool = False,
+                 **kwargs: Any) -> None:
+        super().__init__()
+        self.feature_dim = feature_dim
+        self.heads = heads
+        self.head_dim = head_dim or feature_dim
+        self.negative_slope = negative_slope
+        self.train_attention = train_attention
+        width = self.heads * self.head_dim
+        self.left_right_projection = nn.Linear(feature_dim, 2 * width, bias=bias)
+        self._outer_proj = nn.Linear(width, feature_dim, bias=bias) if out_proj else None
+        self.attn_weights = nn.Parameter(torch.empty(heads, self.head_dim))
+        nn.init.xavier_normal_(self.attn_weights, gain=nn.init.calculate_gain("relu"))
+        self.launch = {k: v for k, v in kwargs.items() if k.endswith("_warps")}
+
+    def forward(self, x: torch.Tensor, graph, **kwargs: Any) -> torch.Tensor:
+        width = self.heads * self.head_dim
+        x_left, x_right = self.left_right_projection(x).split(width, -1)
+        x_left = x_left.view(-1, self.heads, self.head_dim)
+        x_right = x_right.view(-1, self.heads, self.head_dim)
+        attn = self.attn_weights if self.train_attention else self.attn_weights.data
+        if _is_shard(graph):
+            out = tdist.sharded_gatv2_aggr(graph, x_left, x_right, attn, self.negative_slope, **self.launch)
+        else:
+            out = gatv2_aggr(graph, x_left, x_right, attn, self.negative_slope, **self.launch)
+        out = out.reshape(-1, width)
+        return self._outer_proj(out) if self._outer_proj is not None else out
+
+
+class GraphTransformerConv(nn.Module):
+    """LayerNorm -> fused QKV projection -> graph attention (reference: ``_CudaGraphTransformerConv``)."""
+
+    def __init__(self, feature_dim: int, heads: int = 8, **kwargs: Any) -> None:
+        super().__init__()
+        self.feature_dim = feature_dim
+        self.num_heads = heads
+        self.head_dim = feature_dim // heads
+        self.qkv_proj = nn.Linear(feature_dim, 3 * feature_dim)
+        self.attn_scores_multiplier = float(self.head_dim) ** -0.5
+        self.launch = {k: v for k, v in kwargs.items() if k.endswith("_warps")}
+
+    def forward(self, x: torch.Tensor, graph, **kwargs: Any) -> torch.Tensor:
+        x = torch.nn.functional.layer_norm(x, (x.shape[-1],))
+        q, k, v = self.qkv_proj(x).split(self.feature_dim, -1)
+        q, k, v = (t.view(-1, self.num_heads, self.head_dim) for t in (q, k, v))
+        if _is_shard(graph):
+            out = tdist.sharded_graph_transformer_aggr(graph, q, k, v, self.attn_scores_multiplier, **self.launch)
+        else:
+            out = graph_transformer_aggr(graph, x, q, k, v, self.attn_scores_multiplier, **self.launch)
+        return out.reshape(-1, self.feature_dim)
+
+
+class TwoLayerGATv2(nn.Module):
+    """Linear -> ``hidden_heads`` x ``hidden_dim`` GATv2 -> ELU -> Linear -> 1 x ``num_classes`` GATv2."""
+
+    def __init__(self, in_dim: int = 100, hidden_heads: int = 4, hidden_dim: int = 64, num_classes: int = 47,
+                 negative_slope: float = 0.2, seed: int | None = None) -> None:
+        super().__init__()
+        if seed is not None:
+            torch.manual_seed(seed)
+        self.conv1 = GATv2Conv(in_dim, heads=hidden_heads, head_dim=hidden_dim, negative_slope=negative_slope,
+                               out_proj=False, train_attention=True)
+        self.conv2 = GATv2Conv(hidden_heads * hidden_dim, heads=1, head_dim=num_classes,
+                               negative_slope=negative_slope, out_proj=False, train_attention=True)
+        for conv in (self.conv1, self.conv2):
+            nn.init.xavier_uniform_(conv.left_right_projection.weight)
+
+    def forward(self, x: torch.Tensor, graph) -> torch.Tensor:
+        h = torch.nn.functional.elu(self.conv1(x, graph))
+        return self.conv2(h, graph)
