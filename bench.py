@@ -183,44 +183,48 @@ class Job:
 
     # forward + backward on whatever `inputs` / `grad` currently hold
     def step(self):
+        out = self.forward()
+        return out + self.backward(out)
+
+    def forward(self):
+        """The outputs of the forward pass (a tuple; four tensors for the forward-only cfg0)."""
         import turbo_gnn_b200 as tg
         from turbo_gnn_b200 import dist as tdist
 
         g, x = self.graph, self.inputs
         if self.op == "gt":
             if self.shard:
-                out = tdist.sharded_graph_transformer_aggr(self.shard, x[0], x[1], x[2], self.wl.params["scale"],
-                                                           forward_light_warps=1)
-            else:
-                out = tg.graph_transformer_aggr(g, None, x[0], x[1], x[2], self.wl.params["scale"],
-                                                forward_light_warps=1)
-            return (out,) + torch.autograd.grad(out, x, self.grad)
+                return (tdist.sharded_graph_transformer_aggr(self.shard, x[0], x[1], x[2], self.wl.params["scale"],
+                                                             forward_light_warps=1),)
+            return (tg.graph_transformer_aggr(g, None, x[0], x[1], x[2], self.wl.params["scale"],
+                                              forward_light_warps=1),)
         if self.op == "gatv2":
             if self.shard:
-                out = tdist.sharded_gatv2_aggr(self.shard, x[0], x[1], x[2], 0.2)
-            else:
-                out = tg.gatv2_aggr(g, x[0], x[1], x[2], 0.2)
-            return (out,) + torch.autograd.grad(out, x, self.grad)
+                return (tdist.sharded_gatv2_aggr(self.shard, x[0], x[1], x[2], 0.2),)
+            return (tg.gatv2_aggr(g, x[0], x[1], x[2], 0.2),)
         if self.op == "spmm":
             if self.shard:
-                out = tdist.sharded_spmm_aggr(self.shard, x[0], "none", self.scales)
-            else:
-                out = tg.spmm_aggr(x[0], g.forward_indptr, g.forward_indices, "none", -1, 256)
-            return (out,) + torch.autograd.grad(out, x, self.grad)
-        if self.op == "gatv2_model":  # cfg4: two projection + aggregation layers, parameter gradients
-            out = self.model(x[0], self.shard if self.shard else g)
+                return (tdist.sharded_spmm_aggr(self.shard, x[0], "none", self.scales),)
+            return (tg.spmm_aggr(x[0], g.forward_indptr, g.forward_indices, "none", -1, 256),)
+        if self.op == "gatv2_model":  # cfg4: two projection + aggregation layers
+            return (self.model(x[0], self.shard if self.shard else g),)
+        # cfg0: forward only, four reductions
+        return tuple(tg.reduction_aggr(g, x[0], warps_per_block=4, reduce=red) for red in ("min", "max", "sum", "mean"))
+
+    def backward(self, outs):
+        """Gradients of the inputs (of the parameters for cfg4, which are not returned)."""
+        if self.op == "reduce":
+            return ()
+        if self.op == "gatv2_model":
             params = list(self.model.parameters())
-            grads = torch.autograd.grad(out, params, self.grad)
+            grads = torch.autograd.grad(outs[0], params, self.grad)
             if self.shard:
                 import torch.distributed as dist
 
                 flat = torch.cat([gr.reshape(-1) for gr in grads])
                 dist.all_reduce(flat)  # replicated parameters: sum the per-shard gradients
-            return (out,)
-        outs = []
-        for red in ("min", "max", "sum", "mean"):  # cfg0: forward only, four reductions
-            outs.append(tg.reduction_aggr(g, x[0], warps_per_block=4, reduce=red))
-        return tuple(outs)
+            return ()
+        return torch.autograd.grad(outs[0], self.inputs, self.grad)
 
     # ---- byte model: algorithmic bytes per STEP of each library entry point, this rank ----
     def entry_bytes(self):
@@ -487,15 +491,31 @@ def main_ours(args):
             host_grad.numel() * host_grad.element_size() if host_grad is not None else 0)
         d2h = sum(h.numel() * h.element_size() for h in host_out)
 
+        # The upstream gradient comes in while the forward pass runs and the forward result goes
+        # out while the backward pass runs (two side streams); everything is joined before the end.
+        side_in, side_out = torch.cuda.Stream(), torch.cuda.Stream()
+
         def e2e_step():
+            cur = torch.cuda.current_stream()
             with torch.no_grad():
                 for dev_t, h in zip(job.inputs, host_in):
                     dev_t.copy_(h, non_blocking=True)
                 if host_grad is not None:
-                    job.grad.copy_(host_grad, non_blocking=True)
-            res = job.step()
-            for h, o in zip(host_out, res):
+                    side_in.wait_stream(cur)  # the previous step's backward pass has read the old gradient
+                    with torch.cuda.stream(side_in):
+                        job.grad.copy_(host_grad, non_blocking=True)
+            outs = job.forward()
+            n_fwd = len(outs)
+            side_out.wait_stream(cur)
+            with torch.cuda.stream(side_out):
+                for h, o in zip(host_out, outs):
+                    o.record_stream(side_out)
+                    h.copy_(o, non_blocking=True)
+            cur.wait_stream(side_in)
+            grads = job.backward(outs)
+            for h, o in zip(host_out[n_fwd:], grads):
                 h.copy_(o, non_blocking=True)
+            cur.wait_stream(side_out)
 
         for _ in range(2):
             e2e_step()

@@ -61,10 +61,16 @@ typedef enum tgnn_reduce {
     TGNN_REDUCE_MEAN = 3
 } tgnn_reduce;
 
-/* Where a call runs. */
+/* Where a call runs.
+ *
+ * By default a call that has rows in the light tier AND in the heavy / hub tiers runs the two
+ * groups of kernels side by side: the heavy / hub kernels go to a stream the library creates once
+ * per device, forked from and joined back into `stream` with events, so the caller sees plain
+ * stream order.  TGNN_EXEC_SERIAL_TIERS keeps every kernel on `stream`. */
+#define TGNN_EXEC_SERIAL_TIERS 1
 typedef struct tgnn_exec {
     int32_t device; /* CUDA device ordinal that owns every pointer of the call */
-    int32_t _pad;
+    int32_t flags;  /* 0 or TGNN_EXEC_SERIAL_TIERS */
     void *stream;   /* cudaStream_t; NULL = legacy default stream */
 } tgnn_exec;
 
@@ -96,7 +102,7 @@ typedef struct tgnn_schedule {
     const int32_t *chunk_hub;    /* [num_chunks] */
     int64_t num_chunks;
     int32_t chunk_edges;  /* edges per hub chunk, multiple of 32, 32..65536 */
-    int32_t light_warps;  /* warps per CTA in the light tier: 1,2,4,8 */
+    int32_t light_warps;  /* warps per CTA in the light tier: 1,2,4,8 (attention ops: at most 4) */
     int32_t heavy_warps;  /* warps per CTA in the heavy and hub tiers: 1..16 */
     int32_t light_warps_per_row; /* 0 or 1: one warp per light row (light_warps rows per CTA);
                                     2..16: light rows also get a CTA each, of this many warps */

@@ -35,7 +35,7 @@ _ITYPES = {torch.int32: I32, torch.int64: I64, torch.uint32: I32, torch.uint64: 
 
 
 class Exec(C.Structure):
-    _fields_ = [("device", C.c_int32), ("_pad", C.c_int32), ("stream", C.c_void_p)]
+    _fields_ = [("device", C.c_int32), ("flags", C.c_int32), ("stream", C.c_void_p)]
 
 
 class Csr(C.Structure):
@@ -410,11 +410,17 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return t.data_ptr()
 
 
+EXEC_SERIAL_TIERS = 1
+# TURBO_GNN_B200_SERIAL_TIERS=1 keeps every kernel of a call on the caller's stream (the default
+# runs the heavy / hub tiers beside the light tier on a library-owned stream).
+_EXEC_FLAGS = EXEC_SERIAL_TIERS if os.environ.get("TURBO_GNN_B200_SERIAL_TIERS", "0") == "1" else 0
+
+
 def exec_of(t: torch.Tensor) -> Exec:
     if not t.is_cuda:
         raise RuntimeError("turbo_gnn_b200 kernels need CUDA tensors; there is no CPU path")
     dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
-    return Exec(device=dev, stream=torch.cuda.current_stream(dev).cuda_stream)
+    return Exec(device=dev, flags=_EXEC_FLAGS, stream=torch.cuda.current_stream(dev).cuda_stream)
 
 
 def mat_of(t: torch.Tensor) -> Mat:

@@ -24,6 +24,66 @@ int sm_count(int device) {
     return cached[device];
 }
 
+namespace {
+
+struct SideSlot {
+    std::mutex mu;
+    bool ready = false;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t forked = nullptr;
+    cudaEvent_t joined = nullptr;
+};
+
+SideSlot &side_slot(int device) {
+    static SideSlot slots[64];
+    return slots[(device >= 0 && device < 64) ? device : 0];
+}
+
+}  // namespace
+
+TierFork::TierFork(const tgnn_exec &ex, bool wanted)
+    : main_(static_cast<cudaStream_t>(ex.stream)), side_(static_cast<cudaStream_t>(ex.stream)) {
+    if (!wanted || ex.device < 0 || ex.device >= 64) return;
+    SideSlot &slot = side_slot(ex.device);
+    slot.mu.lock();
+    slot_ = &slot;
+    cudaError_t err = cudaSuccess;
+    if (!slot.ready) {
+        err = cudaStreamCreateWithFlags(&slot.stream, cudaStreamNonBlocking);
+        if (err == cudaSuccess) err = cudaEventCreateWithFlags(&slot.forked, cudaEventDisableTiming);
+        if (err == cudaSuccess) err = cudaEventCreateWithFlags(&slot.joined, cudaEventDisableTiming);
+        slot.ready = err == cudaSuccess;
+    }
+    if (err == cudaSuccess) err = cudaEventRecord(slot.forked, main_);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(slot.stream, slot.forked, 0);
+    if (err != cudaSuccess) {
+        status_ = fail(TGNN_ERR_CUDA, "forking the side stream failed: %s (%d)", cudaGetErrorString(err),
+                       static_cast<int>(err));
+        return;
+    }
+    side_ = slot.stream;
+}
+
+int32_t TierFork::join() {
+    if (slot_ == nullptr || side_ == main_) return TGNN_OK;
+    SideSlot &slot = *static_cast<SideSlot *>(slot_);
+    cudaError_t err = cudaEventRecord(slot.joined, side_);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(main_, slot.joined, 0);
+    side_ = main_;
+    if (err != cudaSuccess)
+        return fail(TGNN_ERR_CUDA, "joining the side stream failed: %s (%d)", cudaGetErrorString(err),
+                    static_cast<int>(err));
+    return TGNN_OK;
+}
+
+TierFork::~TierFork() {
+    if (slot_ == nullptr) return;
+    // An early error return between fork and join still has to order the side work before
+    // anything the caller enqueues next.
+    if (side_ != main_) join();
+    static_cast<SideSlot *>(slot_)->mu.unlock();
+}
+
 int32_t check_exec(const tgnn_exec &e) {
     TGNN_REQUIRE(e.device >= 0, TGNN_ERR_INVALID_ARGUMENT, "device ordinal %d is negative", e.device);
     TGNN_CUDA(cudaSetDevice(e.device));

@@ -278,5 +278,6 @@ extern "C" int32_t tgnn_spmm_static_scratch(const tgnn_spmm_args *a) {
     tgnn_spmm_args with_scratch = *a;
     with_scratch.workspace = scratch;
     with_scratch.workspace_bytes = TGNN_STATIC_SCRATCH_BYTES;
+    with_scratch.exec.flags |= TGNN_EXEC_SERIAL_TIERS;  // no library-owned stream or events either
     return tgnn_spmm(&with_scratch);
 }

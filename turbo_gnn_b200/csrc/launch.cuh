@@ -49,6 +49,26 @@ inline bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
 // Number of SMs of a device, cached per ordinal (read-only query).
 int sm_count(int device);
 
+// Runs the heavy / hub kernels of a call beside its light kernel.  Construction forks the
+// device's side stream from `main` (holding a per-device lock, so concurrent host threads
+// cannot interleave their event records); join() makes `main` wait for the side work.
+class TierFork {
+  public:
+    TierFork(const tgnn_exec &ex, bool wanted);
+    ~TierFork();
+    TierFork(const TierFork &) = delete;
+    TierFork &operator=(const TierFork &) = delete;
+    int32_t status() const { return status_; }
+    cudaStream_t side() const { return side_; }  // == main when not forked
+    int32_t join();
+
+  private:
+    cudaStream_t main_;
+    cudaStream_t side_;
+    void *slot_ = nullptr;
+    int32_t status_ = TGNN_OK;
+};
+
 int32_t check_exec(const tgnn_exec &e);
 int32_t check_csr(const tgnn_csr &c);
 int32_t check_schedule(const tgnn_schedule &s, const tgnn_csr &c);
@@ -85,6 +105,41 @@ int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_
     CsrDev<I> c{static_cast<const I *>(csr.indptr), static_cast<const I *>(csr.indices)};
     const int carry_smem = Op::kCarryWords * 32 * static_cast<int>(sizeof(uint32_t));
 
+    // Heavy and hub rows have the long critical paths: they are launched first, on the side
+    // stream when the call also has light rows, and the light tier fills the rest of the GPU.
+    const bool has_big = s.num_heavy > 0 || s.num_hub > 0;
+    TierFork fork(ex, s.num_light > 0 && has_big && (ex.flags & TGNN_EXEC_SERIAL_TIERS) == 0);
+    TGNN_TRY(fork.status());
+    cudaStream_t big = fork.side();
+    HubDev<I> hub{static_cast<const I *>(s.hub_rows), s.hub_part_ptr, s.chunk_hub, s.chunk_edges};
+    const int hw = s.heavy_warps;
+    const size_t merge_smem = static_cast<size_t>(hw > 1 ? hw - 1 : 0) * Op::kWords * 32 * sizeof(uint32_t);
+    if (s.num_hub > 0) {
+        const size_t need = hub_scratch_bytes<Op>(s.num_chunks, geo.slices);
+        TGNN_REQUIRE(scratch != nullptr && scratch_bytes >= need, TGNN_ERR_WORKSPACE,
+                     "hub tier needs %zu bytes of scratch, got %zu", need, scratch_bytes);
+        TGNN_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, TGNN_ERR_WORKSPACE,
+                     "scratch must be 256-byte aligned");
+        uint32_t *partials = static_cast<uint32_t *>(scratch);
+        dim3 grid(static_cast<unsigned>(s.num_chunks), geo.slices);
+        auto k = sweep_heavy_kernel<Op, true>;
+        if (merge_smem > 48 * 1024)
+            TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
+        k<<<grid, hw * 32, merge_smem, big>>>(p, c, nullptr, hub, partials, geo.G);
+        TGNN_CUDA(cudaGetLastError());
+        dim3 mgrid(static_cast<unsigned>((s.num_hub + 3) / 4), geo.slices);
+        hub_merge_kernel<Op><<<mgrid, 128, 0, big>>>(p, c, hub, s.num_hub, partials, geo.G);
+        TGNN_CUDA(cudaGetLastError());
+    }
+    if (s.num_heavy > 0) {
+        dim3 grid(static_cast<unsigned>(s.num_heavy), geo.slices);
+        auto k = sweep_heavy_kernel<Op, false>;
+        if (merge_smem > 48 * 1024)
+            TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
+        k<<<grid, hw * 32, merge_smem, big>>>(p, c, static_cast<const I *>(s.heavy_rows), hub, nullptr, geo.G);
+        TGNN_CUDA(cudaGetLastError());
+    }
+
     HubDev<I> no_hub{nullptr, nullptr, nullptr, 0};
     if (s.num_light > 0 && s.light_warps_per_row > 1) {
         // Light rows as CTA-per-row with a small CTA (the reference's "warps per light row").
@@ -98,6 +153,9 @@ int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_
         TGNN_CUDA(cudaGetLastError());
     } else if (s.num_light > 0) {
         const int warps = s.light_warps;
+        TGNN_REQUIRE(warps * 32 <= Op::kLightMaxThreads, TGNN_ERR_LAUNCH_PARAM,
+                     "Wrong int value: %d light warps per CTA, this op takes at most %d", warps,
+                     Op::kLightMaxThreads / 32);
         int64_t blocks = (s.num_light + warps - 1) / warps;
         if (persistent_light) {
             const int64_t cap = static_cast<int64_t>(sm_count(ex.device)) * (2048 / (warps * 32)) ;
@@ -108,34 +166,7 @@ int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_
             p, c, static_cast<const I *>(s.light_rows), s.num_light, geo.G);
         TGNN_CUDA(cudaGetLastError());
     }
-    HubDev<I> hub{static_cast<const I *>(s.hub_rows), s.hub_part_ptr, s.chunk_hub, s.chunk_edges};
-    const int hw = s.heavy_warps;
-    const size_t merge_smem = static_cast<size_t>(hw > 1 ? hw - 1 : 0) * Op::kWords * 32 * sizeof(uint32_t);
-    if (s.num_heavy > 0) {
-        dim3 grid(static_cast<unsigned>(s.num_heavy), geo.slices);
-        auto k = sweep_heavy_kernel<Op, false>;
-        if (merge_smem > 48 * 1024)
-            TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
-        k<<<grid, hw * 32, merge_smem, stream>>>(p, c, static_cast<const I *>(s.heavy_rows), hub, nullptr, geo.G);
-        TGNN_CUDA(cudaGetLastError());
-    }
-    if (s.num_hub > 0) {
-        const size_t need = hub_scratch_bytes<Op>(s.num_chunks, geo.slices);
-        TGNN_REQUIRE(scratch != nullptr && scratch_bytes >= need, TGNN_ERR_WORKSPACE,
-                     "hub tier needs %zu bytes of scratch, got %zu", need, scratch_bytes);
-        TGNN_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, TGNN_ERR_WORKSPACE,
-                     "scratch must be 256-byte aligned");
-        uint32_t *partials = static_cast<uint32_t *>(scratch);
-        dim3 grid(static_cast<unsigned>(s.num_chunks), geo.slices);
-        auto k = sweep_heavy_kernel<Op, true>;
-        if (merge_smem > 48 * 1024)
-            TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
-        k<<<grid, hw * 32, merge_smem, stream>>>(p, c, nullptr, hub, partials, geo.G);
-        TGNN_CUDA(cudaGetLastError());
-        dim3 mgrid(static_cast<unsigned>((s.num_hub + 3) / 4), geo.slices);
-        hub_merge_kernel<Op><<<mgrid, 128, 0, stream>>>(p, c, hub, s.num_hub, partials, geo.G);
-        TGNN_CUDA(cudaGetLastError());
-    }
+    TGNN_TRY(fork.join());
     return TGNN_OK;
 }
 

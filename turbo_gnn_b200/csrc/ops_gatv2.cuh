@@ -73,7 +73,8 @@ struct Gatv2FwdOp : Gatv2Base<T, I, kVpl> {
     static constexpr int kWords = Acc::kWords;
     static constexpr int kUnroll = kVpl >= 4 ? 2 : 4;
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMinBlocks = TGNN_MIN_BLOCKS_GATV2(kVpl);
+    static constexpr int kLightMaxThreads = TGNN_ATTN_LIGHT_THREADS;
 
     struct Row {
         float l[kVals];
@@ -143,7 +144,8 @@ struct Gatv2BwdDstOp : Gatv2Base<T, I, kVpl> {
     static constexpr int kWords = 2 * kVals;  // grad_l | grad_a
     static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = kVals;
-    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMinBlocks = TGNN_MIN_BLOCKS_GATV2(kVpl);
+    static constexpr int kLightMaxThreads = TGNN_ATTN_LIGHT_THREADS;
 
     struct Row {
         float l[kVals];
@@ -254,7 +256,8 @@ struct Gatv2BwdSrcOp : Gatv2Base<T, I, kVpl> {
     static constexpr int kWords = kVals;
     static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMinBlocks = TGNN_MIN_BLOCKS_GATV2(kVpl);
+    static constexpr int kLightMaxThreads = TGNN_ATTN_LIGHT_THREADS;
 
     struct Row {
         float r[kVals];

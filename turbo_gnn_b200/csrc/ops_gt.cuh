@@ -65,7 +65,8 @@ struct GtFwdOp : GtBase<T, I, kVpl> {
     static constexpr int kWords = Acc::kWords;
     static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMinBlocks = TGNN_MIN_BLOCKS_GT_FWD(kVpl);
+    static constexpr int kLightMaxThreads = TGNN_ATTN_LIGHT_THREADS;
 
     struct Row {
         float k[kVals];  // key span times scale * log2(e)
@@ -143,7 +144,8 @@ struct GtBwdDstOp : GtBase<T, I, kVpl> {
     static constexpr int kWords = kVals;
     static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMinBlocks = TGNN_MIN_BLOCKS_GT_BWD_DST(kVpl);
+    static constexpr int kLightMaxThreads = TGNN_ATTN_LIGHT_THREADS;
 
     struct Row {
         float k[kVals];  // times scale * log2(e)
@@ -230,7 +232,8 @@ struct GtBwdSrcOp : GtBase<T, I, kVpl> {
     static constexpr int kWords = 2 * kVals;  // dq | dv
     static constexpr int kUnroll = TGNN_ATTN_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = TGNN_LIGHT_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMinBlocks = TGNN_MIN_BLOCKS_GT_BWD_SRC(kVpl);
+    static constexpr int kLightMaxThreads = TGNN_ATTN_LIGHT_THREADS;
 
     struct Row {
         float q[kVals];  // times scale * log2(e)

@@ -46,9 +46,10 @@ struct MinMaxOp {
     static constexpr int kVals = kVpl * kPer;
     static constexpr int kIdxWords = sizeof(I) / 4;
     static constexpr int kWords = kVals * (1 + kIdxWords);
-    static constexpr int kUnroll = (kVpl >= 4) ? 2 : 4;
+    static constexpr int kUnroll = TGNN_REDUCE_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = 1;
+    static constexpr int kLightMinBlocks = TGNN_REDUCE_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMaxThreads = 256;
 
     struct Row {};
     struct Carry {};
@@ -192,9 +193,10 @@ struct WeightedSumOp {
     static constexpr int kPer = Elem<T>::kPerChunk;
     static constexpr int kVals = kVpl * kPer;
     static constexpr int kWords = kVals;
-    static constexpr int kUnroll = (kVpl >= 4) ? 2 : 4;
+    static constexpr int kUnroll = TGNN_REDUCE_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = 1;
+    static constexpr int kLightMinBlocks = TGNN_REDUCE_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMaxThreads = 256;
 
     struct Row {};
     struct Carry {};

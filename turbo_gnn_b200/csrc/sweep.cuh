@@ -121,7 +121,7 @@ __device__ __forceinline__ void merge_groups(Op &op, typename Op::State &st, con
 
 // ---- light tier ---------------------------------------------------------------
 template <class Op>
-__global__ void __launch_bounds__(256, Op::kLightMinBlocks) sweep_light_kernel(typename Op::Params p, CsrDev<typename Op::index_t> csr,
+__global__ void __launch_bounds__(Op::kLightMaxThreads, Op::kLightMinBlocks) sweep_light_kernel(typename Op::Params p, CsrDev<typename Op::index_t> csr,
                                                           const typename Op::index_t *__restrict__ rows,
                                                           int64_t n_rows, int G) {
     using I = typename Op::index_t;
