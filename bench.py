@@ -454,6 +454,13 @@ def main_ours(args):
     _abi.trace.reset(False)
     model = job.entry_bytes()
     per_step = {k: per_call[k] * calls_per_step[k] for k in per_call}  # ms of each entry point per step
+    rank_ms = None
+    if world > 1:  # every rank's entry-point times and shard size: shows how even the partition is
+        import torch.distributed as dist
+
+        mine = {"edges": job.local_edges, "rows": job.local_rows, **{k: round(v, 4) for k, v in per_step.items()}}
+        rank_ms = [None] * world
+        dist.all_gather_object(rank_ms, mine)
     top = max((k for k in per_step if k in model), key=lambda k: per_step[k])
     peak, peak_kind = measured_hbm_peak()
     achieved = model[top] / (per_step[top] * 1e-3) / 1e9
@@ -479,6 +486,8 @@ def main_ours(args):
         "calls_per_step": calls_per_step,
         "step_algorithmic_gbs": step_bytes / (ms_step * 1e-3) / 1e9,
     }
+    if rank_ms is not None:
+        roofline["per_rank"] = rank_ms
 
     # end to end: host buffers in, host buffers out, copies inside the timed region
     e2e = None

@@ -38,7 +38,7 @@
 extern "C" {
 #endif
 
-#define TGNN_ABI_VERSION 1
+#define TGNN_ABI_VERSION 2
 
 typedef enum tgnn_status {
     TGNN_OK = 0,
@@ -106,6 +106,20 @@ typedef struct tgnn_schedule {
     int32_t heavy_warps;  /* warps per CTA in the heavy and hub tiers: 1..16 */
     int32_t light_warps_per_row; /* 0 or 1: one warp per light row (light_warps rows per CTA);
                                     2..16: light rows also get a CTA each, of this many warps */
+    /* Column tiling of the light and heavy tiers (the attention ops honour it, the others
+     * ignore it).  With num_tiles >= 2 the columns are cut into num_tiles ranges and the op runs
+     * as num_tiles passes; in pass t every row folds only its edges whose column lies in range t
+     * and its partial result travels between passes through the call's workspace.  All rows
+     * then sweep one column range at a time, which keeps the gathered feature rows of that
+     * range in L2: on graphs whose rows are long (hundreds of edges) and whose gathered matrix
+     * is several times the L2 size this removes most of the DRAM traffic.
+     *   tile_ptr[t * num_rows + r] = first edge of row r whose column is >= the first column
+     * of range t, t = 0 .. num_tiles (so tile_ptr[0..] = indptr[:-1], the last slice =
+     * indptr[1:]); index type of the CSR.  The workspace then has to hold
+     * tgnn_workspace_bytes(...) + tgnn_tile_workspace_bytes(...) bytes, hub partials first. */
+    const void *tile_ptr;
+    int32_t num_tiles; /* 0 or 1: untiled */
+    int32_t _pad;
 } tgnn_schedule;
 
 /* Row-major matrix view; `cols` contiguous elements per row. */
@@ -251,6 +265,10 @@ int32_t tgnn_spmm(const tgnn_spmm_args *a);
  *     partial results; issue them on one stream or order them with events. */
 #define TGNN_STATIC_SCRATCH_BYTES (8u << 20)
 int32_t tgnn_spmm_static_scratch(const tgnn_spmm_args *a);
+
+/* Extra scratch of a column-tiled call (tgnn_schedule.num_tiles >= 2): one parked row state
+ * per row of the CSR.  256-byte aligned sizes; 0 for an op that ignores tiling. */
+size_t tgnn_tile_workspace_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_rows, int64_t feat_cols);
 
 /* ---- attention: shared pieces -------------------------------------------- */
 
@@ -417,6 +435,72 @@ typedef struct tgnn_gt_bwd_src_args {
     size_t workspace_bytes;
 } tgnn_gt_bwd_src_args;
 int32_t tgnn_gt_backward_src(const tgnn_gt_bwd_src_args *a);
+
+/* ---- graph construction ---------------------------------------------------- */
+
+/* The reference builds its graph object with torch ops on whatever device the
+ * edge list lives on (turbo_gnn/graph.py:39-67: argsort of row * N + col,
+ * bincount, cumsum; graph.py:11-36: torch.quantile of the degrees and two
+ * nonzero() calls).  The three calls below do the same work with one radix
+ * sort written for this library; results are identical to the reference's:
+ * CSR entries ordered by (row, column), light / heavy row ids ascending.
+ *
+ * Limits: num_edges < 2^31, num_nodes < 2^31.  All three use caller scratch of
+ * tgnn_graph_workspace_bytes(max number of items sorted) bytes, 256-byte
+ * aligned; none synchronises. */
+size_t tgnn_graph_workspace_bytes(int64_t num_items);
+
+/* COO -> CSR keyed on `row_ids` (pass the destinations for the forward CSR of
+ * the kernels, the sources for the transposed one). */
+typedef struct tgnn_coo_to_csr_args {
+    tgnn_exec exec;
+    const void *row_ids; /* [num_edges], itype_in */
+    const void *col_ids; /* [num_edges], itype_in */
+    int32_t itype_in;
+    int32_t itype_out;
+    int64_t num_edges;
+    int64_t num_nodes;
+    void *indptr;        /* [num_nodes + 1], itype_out */
+    void *indices;       /* [num_edges], itype_out */
+    int32_t *edge_order; /* optional [num_edges]: input position of every CSR entry (equal
+                            (row, column) pairs keep their input order); NULL = not wanted */
+    int32_t *bad_ids;    /* optional device flag, set to 1 when an id lies outside
+                            [0, num_nodes) (such an edge is filed under (0, 0)); else 0 */
+    void *workspace;     /* tgnn_graph_workspace_bytes(num_edges) */
+    size_t workspace_bytes;
+} tgnn_coo_to_csr_args;
+int32_t tgnn_coo_to_csr(const tgnn_coo_to_csr_args *a);
+
+/* out = { k_lo-th smallest degree, k_hi-th smallest degree, largest degree } (ranks
+ * from 0): the inputs of the quantile cut, whose interpolation stays on the host. */
+typedef struct tgnn_degree_order_stats_args {
+    tgnn_exec exec;
+    const void *indptr; /* [num_rows + 1], itype */
+    int32_t itype;
+    int32_t _pad;
+    int64_t num_rows;
+    int64_t k_lo;
+    int64_t k_hi;
+    int64_t *out;    /* device, 3 values */
+    void *workspace; /* tgnn_graph_workspace_bytes(num_rows) */
+    size_t workspace_bytes;
+} tgnn_degree_order_stats_args;
+int32_t tgnn_degree_order_stats(const tgnn_degree_order_stats_args *a);
+
+/* rows_out = ids of the rows with float(degree) < cut in ascending order, then the
+ * others in ascending order; *num_light = how many come first. */
+typedef struct tgnn_partition_rows_args {
+    tgnn_exec exec;
+    const void *indptr; /* [num_rows + 1], itype */
+    int32_t itype;
+    float cut;
+    int64_t num_rows;
+    void *rows_out;     /* [num_rows], itype */
+    int64_t *num_light; /* device, 1 value */
+    void *workspace;    /* tgnn_graph_workspace_bytes(num_rows) */
+    size_t workspace_bytes;
+} tgnn_partition_rows_args;
+int32_t tgnn_partition_rows(const tgnn_partition_rows_args *a);
 
 #ifdef __cplusplus
 } /* extern "C" */

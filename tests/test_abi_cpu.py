@@ -30,6 +30,9 @@ STRUCTS = {
     "tgnn_gt_fwd_args": _abi.GtFwdArgs,
     "tgnn_gt_bwd_dst_args": _abi.GtBwdDstArgs,
     "tgnn_gt_bwd_src_args": _abi.GtBwdSrcArgs,
+    "tgnn_coo_to_csr_args": _abi.CooToCsrArgs,
+    "tgnn_degree_order_stats_args": _abi.DegreeOrderStatsArgs,
+    "tgnn_partition_rows_args": _abi.PartitionRowsArgs,
 }
 
 
@@ -65,6 +68,11 @@ def test_workspace_query_without_gpu():
     a = _abi.workspace_bytes(_abi.OP_REDUCE_MINMAX, torch.float32, torch.int32, 4, 128)
     b = _abi.workspace_bytes(_abi.OP_REDUCE_MINMAX, torch.float32, torch.int64, 4, 128)
     assert b > a > 0
+
+
+def test_graph_workspace_query_without_gpu():
+    small, large = _abi.graph_workspace_bytes(1000), _abi.graph_workspace_bytes(1_000_000)
+    assert small > 0 and large - small >= 24 * (1_000_000 - 1000) - 4096  # two key and two payload buffers
 
 
 def test_invalid_call_returns_status_and_message_not_a_crash():

@@ -70,3 +70,33 @@ def test_bad_chunk_size_raises_runtime_error():
     g = make_graph(random_edges(50, 300, 2), 50, torch.int32, device="cpu")
     with pytest.raises(RuntimeError):
         _schedule.split_tiers(g.forward_indptr, g.forward_light_nodes, g.forward_heavy_nodes, chunk_edges=48)
+
+
+def test_auto_tiles_rule():
+    from turbo_gnn_b200 import _schedule as S
+
+    # 233k nodes x 2 KB gathered per edge, mean degree 492: 477 MB -> 8 tiles
+    assert S.auto_tiles(232_965, 232_965, 114_585_574, 2048) == 8
+    # the same graph cut into 8 row shards keeps the column footprint and the row length
+    assert S.auto_tiles(28_673, 8 * 29_344, 14_321_060, 2048) == 8
+    # short rows, or a gathered matrix that fits L2: one pass
+    assert S.auto_tiles(169_343, 169_343, 2_460_000, 2048) == 1
+    assert S.auto_tiles(20_000, 20_000, 10_000_000, 2048) == 1
+    assert S.auto_tiles(4_194_304, 4_194_304, 65_000_000, 512) == 1
+    assert S.auto_tiles(0, 10, 0, 2048) == 1
+
+
+def test_tile_table_on_host():
+    import torch
+    from turbo_gnn_b200 import _schedule as S
+
+    indptr = torch.tensor([0, 3, 3, 7, 8], dtype=torch.int32)
+    indices = torch.tensor([0, 5, 9, 1, 2, 3, 8, 4], dtype=torch.int32)
+    table = S.build_tile_ptr(indptr, indices, 10, 2).view(3, 4)  # tiles [0,5) and [5,10)
+    assert table.dtype == torch.int32
+    assert table.tolist() == [[0, 3, 3, 7], [1, 3, 6, 8], [3, 3, 7, 8]]
+    sched = S.split_tiers(indptr, torch.arange(4, dtype=torch.int32), torch.zeros(0, dtype=torch.int32))
+    same = S.with_column_tiles(sched, indptr, indices, 10, 2048, tiles=1)
+    assert same is sched and same.num_tiles == 1
+    tiled = S.with_column_tiles(sched, indptr, indices, 10, 2048, tiles=2)
+    assert tiled.num_tiles == 2 and tiled.tile_ptr.numel() == 12 and tiled.light is sched.light

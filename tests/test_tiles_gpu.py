@@ -1,0 +1,62 @@
+"""Column-tiled sweeps of the attention ops: the rows fold one column range per pass and carry
+their state between passes.  Forced tile counts on small graphs (hub rows, rows that are empty
+in some tiles, sub-warp lane groups, CTA-per-row tiers) against the CPU oracle, same bars as the
+untiled tests."""
+
+import pytest
+import torch
+
+from test_attention_gpu import TOL, _gatv2_case, _graph, _gt_case
+from turbo_gnn_b200 import _C, _schedule
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("tiles", [2, 5, 16])
+@pytest.mark.parametrize("h,d", [(4, 64), (2, 16), (1, 256), (3, 32)])
+def test_gt_tiled_matches_oracle(tiles, h, d):
+    ei, g = _graph(torch.int32, 0.9, seed=31)
+    with _C.hub_tier(column_tiles=tiles):
+        errs = _gt_case(ei, g, h, d, torch.float32)
+    assert max(errs.values()) <= TOL[torch.float32], errs
+
+
+@pytest.mark.parametrize("tiles", [2, 7])
+@pytest.mark.parametrize("h,d", [(8, 64), (2, 16), (1, 47)])
+def test_gatv2_tiled_matches_oracle(tiles, h, d):
+    ei, g = _graph(torch.int64, 0.9, seed=32)
+    with _C.hub_tier(column_tiles=tiles):
+        errs = _gatv2_case(ei, g, h, d, torch.float32)
+    assert max(errs.values()) <= TOL[torch.float32], errs
+
+
+@pytest.mark.parametrize("cfg", [dict(cta_min_degree=0, hub_min_degree=1 << 30),          # light + CTA tier
+                                 dict(cta_min_degree=0, hub_min_degree=256, chunk_edges=64),  # hub rows stay untiled
+                                 dict(cta_min_degree=1 << 30, hub_min_degree=1 << 30)])       # everything warp-per-row
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_tiles_with_every_tier(cfg, dt):
+    ei, g = _graph(torch.int32, 0.8, seed=33)
+    with _C.hub_tier(column_tiles=4, **cfg):
+        errs = _gt_case(ei, g, 4, 32, dt)
+        errs.update({"gat_" + k: v for k, v in _gatv2_case(ei, g, 4, 32, dt).items()})
+    assert max(errs.values()) <= TOL[dt], errs
+
+
+def test_tiled_with_light_rows_as_small_ctas():
+    ei, g = _graph(torch.int32, 0.9, seed=34)
+    with _C.hub_tier(column_tiles=3):
+        errs = _gt_case(ei, g, 4, 64, torch.float32, forward_light_warps=2, backward_light_warps=4)
+    assert max(errs.values()) <= TOL[torch.float32], errs
+
+
+def test_tile_table_device_matches_definition():
+    ei, g = _graph(torch.int32, 0.9, seed=35)
+    n = g.forward_indptr.numel() - 1
+    tiles = 6
+    table = _schedule.build_tile_ptr(g.forward_indptr, g.forward_indices, n, tiles).view(tiles + 1, n).cpu()
+    ptr, idx = g.forward_indptr.cpu().long(), g.forward_indices.cpu().long()
+    span = (n + tiles - 1) // tiles
+    for r in (0, 1, 2, n // 2, n - 1):
+        cols = idx[ptr[r]: ptr[r + 1]]
+        for t in range(tiles + 1):
+            assert int(table[t, r]) == int(ptr[r]) + int((cols < t * span).sum())

@@ -40,11 +40,13 @@ _hub_cfg = {
     "hub_min_degree": _schedule.DEFAULT_HUB_MIN_DEGREE,
     "cta_min_degree": _schedule.DEFAULT_CTA_MIN_DEGREE,
     "sort_by_degree": True,
+    "column_tiles": None,  # attention ops: None = automatic, 1 = off, k = k column tiles
 }
 
 
 def configure_hub_tier(**values) -> dict:
-    """Set tier parameters (``chunk_edges``, ``hub_min_degree``, ``cta_min_degree``, ``sort_by_degree``)
+    """Set tier parameters (``chunk_edges``, ``hub_min_degree``, ``cta_min_degree``, ``sort_by_degree``,
+    ``column_tiles``)
     for later calls; a value of ``None`` selects the automatic threshold.  Returns the previous values."""
     unknown = set(values) - set(_hub_cfg)
     if unknown:
@@ -80,6 +82,13 @@ def _sched(indptr, light, heavy, chunk_edges="cfg", slots=_schedule.ATTENTION_WA
                                   _hub_cfg["sort_by_degree"], _hub_cfg["cta_min_degree"], slots)
 
 
+def _attn_sched(indptr, indices, light, heavy, num_cols: int, gather_bytes: int):
+    """Tier schedule of an attention sweep plus, where it pays, the column-tile table
+    (`gather_bytes` = bytes of feature rows gathered per edge)."""
+    sched = _sched(indptr, light, heavy)
+    return _schedule.with_column_tiles(sched, indptr, indices, num_cols, gather_bytes, _hub_cfg["column_tiles"])
+
+
 def _check_index_family(indptr, *others):
     for t in others:
         if t.dtype != indptr.dtype:
@@ -88,8 +97,11 @@ def _check_index_family(indptr, *others):
             raise RuntimeError("index tensors must be CUDA tensors")
 
 
-def _scratch(op: int, sched: _schedule.TierSchedule, feat: torch.Tensor, itype: torch.dtype, cols: int):
+def _scratch(op: int, sched: _schedule.TierSchedule, feat: torch.Tensor, itype: torch.dtype, cols: int,
+             num_rows: int = 0):
     need = _abi.workspace_bytes(op, feat.dtype, itype, sched.num_chunks, cols) if sched.num_chunks else 0
+    if sched.num_tiles > 1:  # parked row states of a column-tiled call, after the hub partials
+        need += _abi.tile_workspace_bytes(op, feat.dtype, itype, num_rows, cols)
     if need == 0:
         return None, 0
     buf = torch.empty(need, dtype=torch.uint8, device=feat.device)
@@ -522,8 +534,9 @@ def gatv2_forward(l, r, row_ptr, col_idx, attn_vec, negative_slope, light_nodes,
     out = torch.empty((n_rows, heads, dp), dtype=l.dtype, device=l.device)
     lse = torch.empty((n_rows, heads), dtype=torch.float32, device=l.device)
     if n_rows > 0:
-        sched = _sched(row_ptr, light_nodes, heavy_nodes)
-        ws, ws_bytes = _scratch(_abi.OP_GATV2_FWD, sched, l_in, row_ptr.dtype, heads * dp)
+        sched = _attn_sched(row_ptr, col_idx, light_nodes, heavy_nodes, r.shape[0],
+                            heads * dp * r_in.element_size())
+        ws, ws_bytes = _scratch(_abi.OP_GATV2_FWD, sched, l_in, row_ptr.dtype, heads * dp, n_rows)
         args = _abi.Gatv2FwdArgs(
             exec=_abi.exec_of(l_in),
             csr=_abi.csr_of(row_ptr, col_idx, r.shape[0]),
@@ -558,8 +571,9 @@ def gatv2_backward_dst(grad_h, l, r, row_ptr, col_idx, attn_vec, lse, G, negativ
     if grad_attn_f32 is None:
         grad_attn_f32 = torch.zeros((heads, dp), dtype=torch.float32, device=l.device)
     if n_rows > 0:
-        sched = _sched(row_ptr, light_nodes, heavy_nodes)
-        ws, ws_bytes = _scratch(_abi.OP_GATV2_BWD_DST, sched, l_in, row_ptr.dtype, heads * dp)
+        sched = _attn_sched(row_ptr, col_idx, light_nodes, heavy_nodes, r.shape[0],
+                            heads * dp * r_in.element_size())
+        ws, ws_bytes = _scratch(_abi.OP_GATV2_BWD_DST, sched, l_in, row_ptr.dtype, heads * dp, row_ptr.numel() - 1)
         args = _abi.Gatv2BwdDstArgs(
             exec=_abi.exec_of(l_in),
             csr=_abi.csr_of(row_ptr, col_idx, r.shape[0]),
@@ -595,8 +609,10 @@ def gatv2_backward_src(grad_h, l, r, row_ptr_T, col_idx_T, attn_vec, lse, G, neg
     a_in = _as_rows(_pad_cols(attn_vec, dp), 32)
     grad_r = torch.empty((n_src, heads, dp), dtype=r.dtype, device=r.device)
     if n_src > 0:
-        sched = _sched(row_ptr_T, light_nodes, heavy_nodes)
-        ws, ws_bytes = _scratch(_abi.OP_GATV2_BWD_SRC, sched, r_in, row_ptr_T.dtype, heads * dp)
+        sched = _attn_sched(row_ptr_T, col_idx_T, light_nodes, heavy_nodes, l.shape[0],
+                            2 * heads * dp * r_in.element_size())
+        ws, ws_bytes = _scratch(_abi.OP_GATV2_BWD_SRC, sched, r_in, row_ptr_T.dtype, heads * dp,
+                                row_ptr_T.numel() - 1)
         args = _abi.Gatv2BwdSrcArgs(
             exec=_abi.exec_of(r_in),
             csr_t=_abi.csr_of(row_ptr_T, col_idx_T, l.shape[0]),
@@ -669,8 +685,9 @@ def gt_forward_csr_mh(row_ptr, col_idx, Q, K, V, scale, light_nodes, heavy_nodes
     out = torch.empty((n_rows, heads, dp), dtype=Q.dtype, device=Q.device)
     lse = torch.empty((n_rows, heads), dtype=torch.float32, device=Q.device)
     if n_rows > 0:
-        sched = _sched(row_ptr, light_nodes, heavy_nodes)
-        ws, ws_bytes = _scratch(_abi.OP_GT_FWD, sched, q_in, row_ptr.dtype, heads * dp)
+        sched = _attn_sched(row_ptr, col_idx, light_nodes, heavy_nodes, Q.shape[0],
+                            2 * heads * dp * q_in.element_size())
+        ws, ws_bytes = _scratch(_abi.OP_GT_FWD, sched, q_in, row_ptr.dtype, heads * dp, row_ptr.numel() - 1)
         args = _abi.GtFwdArgs(
             exec=_abi.exec_of(q_in),
             csr=_abi.csr_of(row_ptr, col_idx, Q.shape[0]),
@@ -698,8 +715,9 @@ def gt_backward_dst(row_ptr, col_idx, Q, K, V, dO, lse, delta, scale, light_node
     q_in, k_in, v_in, g_in = _head_rows(Q, dp), _head_rows(K, dp), _head_rows(V, dp), _head_rows(dO, dp)
     dk = torch.empty((n_rows, heads, dp), dtype=K.dtype, device=K.device)
     if n_rows > 0:
-        sched = _sched(row_ptr, light_nodes, heavy_nodes)
-        ws, ws_bytes = _scratch(_abi.OP_GT_BWD_DST, sched, k_in, row_ptr.dtype, heads * dp)
+        sched = _attn_sched(row_ptr, col_idx, light_nodes, heavy_nodes, Q.shape[0],
+                            2 * heads * dp * k_in.element_size())
+        ws, ws_bytes = _scratch(_abi.OP_GT_BWD_DST, sched, k_in, row_ptr.dtype, heads * dp, row_ptr.numel() - 1)
         args = _abi.GtBwdDstArgs(
             exec=_abi.exec_of(k_in),
             csr=_abi.csr_of(row_ptr, col_idx, Q.shape[0]),
@@ -733,8 +751,10 @@ def gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_
     dq = torch.empty((n_src, heads, dp), dtype=Q.dtype, device=Q.device)
     dv = torch.empty((n_src, heads, dp), dtype=Q.dtype, device=Q.device)
     if n_src > 0:
-        sched = _sched(row_ptr_T, light_nodes, heavy_nodes)
-        ws, ws_bytes = _scratch(_abi.OP_GT_BWD_SRC, sched, q_in, row_ptr_T.dtype, heads * dp)
+        sched = _attn_sched(row_ptr_T, col_idx_T, light_nodes, heavy_nodes, K.shape[0],
+                            2 * heads * dp * q_in.element_size())
+        ws, ws_bytes = _scratch(_abi.OP_GT_BWD_SRC, sched, q_in, row_ptr_T.dtype, heads * dp,
+                                row_ptr_T.numel() - 1)
         args = _abi.GtBwdSrcArgs(
             exec=_abi.exec_of(q_in),
             csr_t=_abi.csr_of(row_ptr_T, col_idx_T, K.shape[0]),

@@ -19,7 +19,7 @@ from pathlib import Path
 import torch
 
 LIB_NAME = "libturbo_gnn_b200.so"
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 OK = 0
 F32, F16, BF16 = 0, 1, 2
@@ -65,6 +65,9 @@ class Schedule(C.Structure):
         ("light_warps", C.c_int32),
         ("heavy_warps", C.c_int32),
         ("light_warps_per_row", C.c_int32),
+        ("tile_ptr", C.c_void_p),
+        ("num_tiles", C.c_int32),
+        ("_pad", C.c_int32),
     ]
 
 
@@ -268,10 +271,58 @@ class GtBwdSrcArgs(C.Structure):
 
 
 # symbol -> argument struct (None = takes no struct); every symbol the header declares.
+class CooToCsrArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("row_ids", C.c_void_p),
+        ("col_ids", C.c_void_p),
+        ("itype_in", C.c_int32),
+        ("itype_out", C.c_int32),
+        ("num_edges", C.c_int64),
+        ("num_nodes", C.c_int64),
+        ("indptr", C.c_void_p),
+        ("indices", C.c_void_p),
+        ("edge_order", C.c_void_p),
+        ("bad_ids", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class DegreeOrderStatsArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("indptr", C.c_void_p),
+        ("itype", C.c_int32),
+        ("_pad", C.c_int32),
+        ("num_rows", C.c_int64),
+        ("k_lo", C.c_int64),
+        ("k_hi", C.c_int64),
+        ("out", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class PartitionRowsArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("indptr", C.c_void_p),
+        ("itype", C.c_int32),
+        ("cut", C.c_float),
+        ("num_rows", C.c_int64),
+        ("rows_out", C.c_void_p),
+        ("num_light", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
 ENTRY_POINTS = {
     "tgnn_abi_version": None,
     "tgnn_last_error": None,
     "tgnn_workspace_bytes": None,
+    "tgnn_tile_workspace_bytes": None,
     "tgnn_segment_reduce_forward": SegmentReduceArgs,
     "tgnn_segment_reduce_backward": SegmentReduceBwdArgs,
     "tgnn_degree_norm": DegreeNormArgs,
@@ -284,6 +335,10 @@ ENTRY_POINTS = {
     "tgnn_gt_forward": GtFwdArgs,
     "tgnn_gt_backward_dst": GtBwdDstArgs,
     "tgnn_gt_backward_src": GtBwdSrcArgs,
+    "tgnn_graph_workspace_bytes": None,
+    "tgnn_coo_to_csr": CooToCsrArgs,
+    "tgnn_degree_order_stats": DegreeOrderStatsArgs,
+    "tgnn_partition_rows": PartitionRowsArgs,
 }
 
 _lib = None
@@ -317,6 +372,10 @@ def load_library() -> C.CDLL:
         lib.tgnn_last_error.argtypes = [C.c_char_p, C.c_size_t]
         lib.tgnn_workspace_bytes.restype = C.c_size_t
         lib.tgnn_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]
+        lib.tgnn_tile_workspace_bytes.restype = C.c_size_t
+        lib.tgnn_tile_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]
+        lib.tgnn_graph_workspace_bytes.restype = C.c_size_t
+        lib.tgnn_graph_workspace_bytes.argtypes = [C.c_int64]
         for name, struct in ENTRY_POINTS.items():
             fn = getattr(lib, name)  # AttributeError here = header and binary disagree
             if struct is not None:
@@ -364,7 +423,8 @@ def _kernels_of(args: C.Structure) -> int:
     sched = getattr(args, "sched", None)
     if sched is None:
         return 1
-    return int(sched.num_light > 0) + int(sched.num_heavy > 0) + 2 * int(sched.num_hub > 0)
+    passes = max(int(sched.num_tiles), 1)
+    return passes * (int(sched.num_light > 0) + int(sched.num_heavy > 0)) + 2 * int(sched.num_hub > 0)
 
 
 def call(name: str, args: C.Structure) -> None:
@@ -381,6 +441,14 @@ def call(name: str, args: C.Structure) -> None:
         status = fn(C.byref(args))
     if status != OK:
         raise RuntimeError(f"{name} failed with status {status}: {last_error()}")
+
+
+def tile_workspace_bytes(op: int, dtype: torch.dtype, itype: torch.dtype, num_rows: int, cols: int) -> int:
+    return int(load_library().tgnn_tile_workspace_bytes(op, dtype_code(dtype), itype_code(itype), num_rows, cols))
+
+
+def graph_workspace_bytes(num_items: int) -> int:
+    return int(load_library().tgnn_graph_workspace_bytes(int(num_items)))
 
 
 def workspace_bytes(op: int, dtype: torch.dtype, itype: torch.dtype, num_chunks: int, cols: int) -> int:

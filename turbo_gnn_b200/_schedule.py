@@ -26,6 +26,7 @@ The chunk tables are small device tensors built with torch ops and cached per
 
 from __future__ import annotations
 
+import dataclasses
 import weakref
 from collections import OrderedDict
 from dataclasses import dataclass
@@ -57,6 +58,8 @@ class TierSchedule:
     chunk_hub: torch.Tensor  # int32 [num_chunks]
     num_chunks: int
     chunk_edges: int
+    tile_ptr: torch.Tensor | None = None  # [(num_tiles + 1) * num_rows], index dtype of the CSR
+    num_tiles: int = 1
 
     def to_struct(self, light_warps: int, heavy_warps: int, light_warps_per_row: int = 1) -> _abi.Schedule:
         """`light_warps` rows share a CTA in the warp-per-row tier; `light_warps_per_row` > 1 gives
@@ -75,6 +78,8 @@ class TierSchedule:
             chunk_edges=self.chunk_edges,
             light_warps=int(light_warps),
             heavy_warps=int(heavy_warps),
+            tile_ptr=_abi.ptr(self.tile_ptr) if self.num_tiles > 1 else None,
+            num_tiles=int(self.num_tiles),
         )
 
 
@@ -100,6 +105,44 @@ def auto_thresholds(num_edges: int, device: torch.device,
     hub_min = max(2048, 4 * fair)
     chunk = min(max(fair // 2, 1024), 32768) // 32 * 32
     return chunk, hub_min, cta_min
+
+
+# Column tiling (see `tgnn_schedule.tile_ptr` in the header).  A tile should hold about half of
+# what L2 keeps of the gathered rows, and a row should still have a few dozen edges per tile so
+# that picking up and parking its state stays a small part of the work.
+L2_BYTES = 126 << 20
+TILE_TARGET_BYTES = 60 << 20
+TILE_MIN_EDGES_PER_ROW = 48
+MAX_TILES = 16
+
+
+def auto_tiles(num_rows: int, num_cols: int, num_edges: int, gather_bytes_per_col: int) -> int:
+    """Number of column tiles for a sweep that gathers `gather_bytes_per_col` bytes per edge."""
+    if num_rows <= 0 or gather_bytes_per_col <= 0:
+        return 1
+    footprint = num_cols * gather_bytes_per_col
+    mean_degree = num_edges / num_rows
+    if footprint < 2 * L2_BYTES or mean_degree < 2 * TILE_MIN_EDGES_PER_ROW:
+        return 1
+    tiles = min(round(footprint / TILE_TARGET_BYTES), int(mean_degree // TILE_MIN_EDGES_PER_ROW), MAX_TILES)
+    return tiles if tiles >= 2 else 1
+
+
+def build_tile_ptr(indptr: torch.Tensor, indices: torch.Tensor, num_cols: int, tiles: int) -> torch.Tensor:
+    """``[(tiles + 1) * num_rows]``: entry ``t * num_rows + r`` is the first edge of row ``r`` whose
+    column is at or beyond the first column of tile ``t`` (tiles are equal ranges of column ids;
+    columns are sorted inside a row)."""
+    ptr, idx = _signed(indptr), _signed(indices)
+    rows = ptr.numel() - 1
+    span = max((num_cols + tiles - 1) // tiles, 1)
+    deg = (ptr[1:] - ptr[:-1]).long()
+    row_of_edge = torch.repeat_interleave(torch.arange(rows, device=ptr.device), deg, output_size=idx.numel())
+    key = torch.div(idx, span, rounding_mode="floor").long().clamp_(max=tiles - 1) * rows + row_of_edge
+    del row_of_edge
+    counts = torch.bincount(key, minlength=tiles * rows).view(tiles, rows)
+    del key
+    ends = ptr[:-1].long().unsqueeze(0) + torch.cumsum(counts, 0)
+    return torch.cat([ptr[:-1].long().unsqueeze(0), ends], 0).to(ptr.dtype).reshape(-1).contiguous()
 
 
 def split_tiers(
@@ -223,5 +266,51 @@ def get_schedule(
                       slots_per_sm)
 
 
+class _TileCache:
+    """Tile tables keyed on the identity of the CSR arrays (they do not depend on the tiers)."""
+
+    def __init__(self, slots: int = 32):
+        self._slots = slots
+        self._items: OrderedDict[tuple, tuple] = OrderedDict()
+
+    def get(self, indptr, indices, num_cols: int, tiles: int) -> torch.Tensor:
+        key = (id(indptr), id(indices), int(num_cols), int(tiles))
+        hit = self._items.get(key)
+        if hit is not None:
+            refs, table = hit
+            if refs[0]() is indptr and refs[1]() is indices:
+                self._items.move_to_end(key)
+                return table
+            del self._items[key]
+        table = build_tile_ptr(indptr, indices, num_cols, tiles)
+        self._items[key] = ((weakref.ref(indptr), weakref.ref(indices)), table)
+        while len(self._items) > self._slots:
+            self._items.popitem(last=False)
+        return table
+
+    def clear(self) -> None:
+        self._items.clear()
+
+
+_tile_cache = _TileCache()
+
+
+def with_column_tiles(sched: TierSchedule, indptr: torch.Tensor, indices: torch.Tensor, num_cols: int,
+                      gather_bytes_per_col: int, tiles: int | None = None) -> TierSchedule:
+    """`sched` with a column-tile table attached; ``tiles=None`` lets :func:`auto_tiles` decide,
+    1 turns tiling off.  The table is cached per CSR."""
+    rows = indptr.numel() - 1
+    if tiles is None:
+        tiles = auto_tiles(rows, num_cols, indices.numel(), gather_bytes_per_col)
+    tiles = int(tiles)
+    if tiles < 1 or tiles > 64:
+        raise RuntimeError(f"Wrong int value: column_tiles={tiles} must be in [1, 64]")
+    if tiles == 1 or rows == 0 or indices.numel() == 0:
+        return sched
+    table = _tile_cache.get(indptr, indices, num_cols, tiles)
+    return dataclasses.replace(sched, tile_ptr=table, num_tiles=tiles)
+
+
 def clear_schedule_cache() -> None:
     _cache.clear()
+    _tile_cache.clear()

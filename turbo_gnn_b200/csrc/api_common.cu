@@ -198,7 +198,25 @@ int32_t check_attn_mat(const tgnn_mat &m, const char *name, int64_t rows, int64_
     return TGNN_OK;
 }
 
+static size_t state_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t slots, int64_t feat_cols) {
+    switch (op) {
+        case TGNN_OP_REDUCE_MINMAX:
+        case TGNN_OP_WEIGHTED_SUM: return tgnn::reduce_scratch_bytes(op, dtype, itype, slots, feat_cols);
+        case TGNN_OP_GATV2_FWD:
+        case TGNN_OP_GATV2_BWD_DST:
+        case TGNN_OP_GATV2_BWD_SRC: return tgnn::gatv2_scratch_bytes(op, dtype, itype, slots, feat_cols);
+        case TGNN_OP_GT_FWD:
+        case TGNN_OP_GT_BWD_DST:
+        case TGNN_OP_GT_BWD_SRC: return tgnn::gt_scratch_bytes(op, dtype, itype, slots, feat_cols);
+        default: return 0;
+    }
+}
+static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
+
 }  // namespace tgnn
+
+using tgnn::round256;
+using tgnn::state_bytes;
 
 extern "C" {
 
@@ -212,17 +230,13 @@ void tgnn_last_error(char *buf, size_t buf_len) {
 
 size_t tgnn_workspace_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_chunks, int64_t feat_cols) {
     if (num_chunks <= 0 || feat_cols <= 0) return 0;
-    switch (op) {
-        case TGNN_OP_REDUCE_MINMAX:
-        case TGNN_OP_WEIGHTED_SUM: return tgnn::reduce_scratch_bytes(op, dtype, itype, num_chunks, feat_cols);
-        case TGNN_OP_GATV2_FWD:
-        case TGNN_OP_GATV2_BWD_DST:
-        case TGNN_OP_GATV2_BWD_SRC: return tgnn::gatv2_scratch_bytes(op, dtype, itype, num_chunks, feat_cols);
-        case TGNN_OP_GT_FWD:
-        case TGNN_OP_GT_BWD_DST:
-        case TGNN_OP_GT_BWD_SRC: return tgnn::gt_scratch_bytes(op, dtype, itype, num_chunks, feat_cols);
-        default: return 0;
-    }
+    return round256(state_bytes(op, dtype, itype, num_chunks, feat_cols));
+}
+
+size_t tgnn_tile_workspace_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_rows, int64_t feat_cols) {
+    if (num_rows <= 0 || feat_cols <= 0) return 0;
+    if (op == TGNN_OP_REDUCE_MINMAX || op == TGNN_OP_WEIGHTED_SUM) return 0;  // these ops are never tiled
+    return round256(state_bytes(op, dtype, itype, num_rows, feat_cols));
 }
 
 }  // extern "C"

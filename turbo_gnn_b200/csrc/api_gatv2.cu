@@ -142,7 +142,7 @@ extern "C" int32_t tgnn_gatv2_forward(const tgnn_gatv2_fwd_args *a) {
         p.ldo = a->out.row_stride;
         p.lse_out = a->lse;
         return run_tiers<Gatv2FwdOp<T, I, decltype(vt)::value>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
-                                                                a->workspace_bytes, false);
+                                                                a->workspace_bytes, false, true);
     });
 }
 
@@ -176,7 +176,7 @@ extern "C" int32_t tgnn_gatv2_backward_dst(const tgnn_gatv2_bwd_dst_args *a) {
         p.ldo = a->grad_l.row_stride;
         p.grad_attn = a->grad_attn_f32;
         return run_tiers<Gatv2BwdDstOp<T, I, decltype(vt)::value>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
-                                                                   a->workspace_bytes, true);
+                                                                   a->workspace_bytes, true, true);
     });
 }
 
@@ -208,6 +208,6 @@ extern "C" int32_t tgnn_gatv2_backward_src(const tgnn_gatv2_bwd_src_args *a) {
         p.out = static_cast<T *>(a->grad_r.data);
         p.ldo = a->grad_r.row_stride;
         return run_tiers<Gatv2BwdSrcOp<T, I, decltype(vt)::value>>(p, a->csr_t, a->sched, a->exec, geo, a->workspace,
-                                                                   a->workspace_bytes, false);
+                                                                   a->workspace_bytes, false, true);
     });
 }

@@ -1,0 +1,247 @@
+// C-ABI entry points of the graph construction: COO -> CSR, degree order statistics and the
+// light / heavy row partition.
+#include "graph_build.cuh"
+#include "launch.cuh"
+
+namespace tgnn {
+
+namespace {
+
+constexpr size_t kAlign = 256;
+inline size_t round_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+struct SortGeometry {
+    int64_t tiles_per_cta;
+    int ctas;
+};
+
+// CTAs own contiguous key ranges; at most 8 CTAs per SM keeps the [digit][CTA] table small
+// enough for the single-CTA scan.
+SortGeometry sort_geometry(int64_t n, int sms) {
+    const int64_t tiles = (n + gb::kTile - 1) / gb::kTile;
+    const int64_t max_ctas = static_cast<int64_t>(sms) * 8;
+    SortGeometry g;
+    g.tiles_per_cta = tiles > max_ctas ? (tiles + max_ctas - 1) / max_ctas : 1;
+    g.ctas = static_cast<int>((tiles + g.tiles_per_cta - 1) / g.tiles_per_cta);
+    if (g.ctas < 1) g.ctas = 1;
+    return g;
+}
+
+// Scratch carved up for one sort of up to `n` items.
+struct SortScratch {
+    uint32_t *hist;
+    uint64_t *keys[2];
+    uint32_t *vals[2];
+    int64_t *small;  // 8 int64 of results / flags
+};
+
+constexpr int kMaxCtas = 148 * 8 * 2;  // table size is fixed so that the query needs no device
+
+size_t sort_scratch_bytes(int64_t n) {
+    const size_t items = static_cast<size_t>(n > 0 ? n : 1);
+    return round_up(64) + round_up(sizeof(uint32_t) * gb::kRadix * kMaxCtas) + 2 * round_up(items * 8) +
+           2 * round_up(items * 4);
+}
+
+SortScratch carve(void *ws, int64_t n) {
+    const size_t items = static_cast<size_t>(n > 0 ? n : 1);
+    unsigned char *p = static_cast<unsigned char *>(ws);
+    SortScratch s;
+    s.small = reinterpret_cast<int64_t *>(p);
+    p += round_up(64);
+    s.hist = reinterpret_cast<uint32_t *>(p);
+    p += round_up(sizeof(uint32_t) * gb::kRadix * kMaxCtas);
+    s.keys[0] = reinterpret_cast<uint64_t *>(p);
+    p += round_up(items * 8);
+    s.keys[1] = reinterpret_cast<uint64_t *>(p);
+    p += round_up(items * 8);
+    s.vals[0] = reinterpret_cast<uint32_t *>(p);
+    p += round_up(items * 4);
+    s.vals[1] = reinterpret_cast<uint32_t *>(p);
+    return s;
+}
+
+int bits_of(uint64_t v) {
+    int b = 0;
+    while (v != 0) {
+        ++b;
+        v >>= 1;
+    }
+    return b > 0 ? b : 1;
+}
+
+// Stable LSD radix sort of keys[0] (and vals[0]) on the low `key_bits` bits; `*where` is the
+// index (0 / 1) of the buffers that hold the result.
+int32_t radix_sort(const SortScratch &s, int64_t n, int key_bits, bool with_vals, const tgnn_exec &ex, int *where) {
+    cudaStream_t stream = static_cast<cudaStream_t>(ex.stream);
+    int cur = 0;
+    if (n > 0) {
+        SortGeometry g = sort_geometry(n, sm_count(ex.device));
+        TGNN_REQUIRE(g.ctas <= kMaxCtas, TGNN_ERR_UNSUPPORTED, "sort grid of %d CTAs exceeds the table of %d", g.ctas,
+                     kMaxCtas);
+        for (int shift = 0; shift < key_bits; shift += 8) {
+            gb::radix_hist_kernel<<<g.ctas, gb::kSortThreads, 0, stream>>>(s.keys[cur], n, shift, g.tiles_per_cta,
+                                                                           s.hist);
+            TGNN_CUDA(cudaGetLastError());
+            gb::scan_counters_kernel<<<1, 1024, 0, stream>>>(s.hist, static_cast<int64_t>(gb::kRadix) * g.ctas);
+            TGNN_CUDA(cudaGetLastError());
+            gb::radix_scatter_kernel<<<g.ctas, gb::kSortThreads, 0, stream>>>(
+                s.keys[cur], s.keys[cur ^ 1], with_vals ? s.vals[cur] : nullptr, with_vals ? s.vals[cur ^ 1] : nullptr, n,
+                shift, g.tiles_per_cta, s.hist);
+            TGNN_CUDA(cudaGetLastError());
+            cur ^= 1;
+        }
+    }
+    *where = cur;
+    return TGNN_OK;
+}
+
+int grid_for(int64_t n, int device) {
+    int64_t blocks = (n + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sm_count(device)) * 16;
+    if (blocks > cap) blocks = cap;
+    return static_cast<int>(blocks > 0 ? blocks : 1);
+}
+
+int32_t check_scratch(const void *ws, size_t bytes, int64_t items) {
+    const size_t need = sort_scratch_bytes(items);
+    TGNN_REQUIRE(ws != nullptr && bytes >= need, TGNN_ERR_WORKSPACE, "graph construction needs %zu bytes of scratch, got %zu",
+                 need, bytes);
+    TGNN_REQUIRE((reinterpret_cast<uintptr_t>(ws) & (kAlign - 1)) == 0, TGNN_ERR_WORKSPACE,
+                 "scratch must be 256-byte aligned");
+    return TGNN_OK;
+}
+
+int32_t check_itype(int32_t it, const char *what) {
+    TGNN_REQUIRE(it == TGNN_I32 || it == TGNN_I64, TGNN_ERR_INVALID_ARGUMENT, "%s: unknown index type %d", what, it);
+    return TGNN_OK;
+}
+
+constexpr int64_t kMaxItems = (1ll << 31) - 1;
+
+}  // namespace
+
+}  // namespace tgnn
+
+using namespace tgnn;
+
+extern "C" size_t tgnn_graph_workspace_bytes(int64_t num_items) { return sort_scratch_bytes(num_items); }
+
+extern "C" int32_t tgnn_coo_to_csr(const tgnn_coo_to_csr_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));
+    TGNN_TRY(check_itype(a->itype_in, "edge ids"));
+    TGNN_TRY(check_itype(a->itype_out, "csr arrays"));
+    TGNN_REQUIRE(a->num_edges >= 0 && a->num_edges <= kMaxItems, TGNN_ERR_UNSUPPORTED,
+                 "num_edges %lld outside [0, 2^31)", static_cast<long long>(a->num_edges));
+    TGNN_REQUIRE(a->num_nodes >= 0 && a->num_nodes <= kMaxItems, TGNN_ERR_UNSUPPORTED,
+                 "num_nodes %lld outside [0, 2^31)", static_cast<long long>(a->num_nodes));
+    TGNN_REQUIRE(a->indptr != nullptr, TGNN_ERR_INVALID_ARGUMENT, "indptr is null");
+    TGNN_REQUIRE(a->num_edges == 0 || (a->row_ids != nullptr && a->col_ids != nullptr && a->indices != nullptr),
+                 TGNN_ERR_INVALID_ARGUMENT, "edge arrays are null");
+    TGNN_REQUIRE(a->num_edges == 0 || a->num_nodes > 0, TGNN_ERR_INVALID_ARGUMENT, "edges without nodes");
+    TGNN_TRY(check_scratch(a->workspace, a->workspace_bytes, a->num_edges));
+    cudaStream_t stream = static_cast<cudaStream_t>(a->exec.stream);
+    const SortScratch s = carve(a->workspace, a->num_edges);
+    const int64_t n = a->num_edges;
+    const uint64_t nodes = static_cast<uint64_t>(a->num_nodes);
+    int32_t *bad = a->bad_ids != nullptr ? a->bad_ids : reinterpret_cast<int32_t *>(s.small);
+    TGNN_CUDA(cudaMemsetAsync(bad, 0, sizeof(int32_t), stream));
+    const bool want_order = a->edge_order != nullptr;
+    int where = 0;
+    if (n > 0) {
+        const int grid = grid_for(n, a->exec.device);
+        if (a->itype_in == TGNN_I32)
+            gb::pack_edge_keys_kernel<int32_t><<<grid, 256, 0, stream>>>(
+                static_cast<const int32_t *>(a->row_ids), static_cast<const int32_t *>(a->col_ids), n, nodes, s.keys[0],
+                want_order ? s.vals[0] : nullptr, bad);
+        else
+            gb::pack_edge_keys_kernel<int64_t><<<grid, 256, 0, stream>>>(
+                static_cast<const int64_t *>(a->row_ids), static_cast<const int64_t *>(a->col_ids), n, nodes, s.keys[0],
+                want_order ? s.vals[0] : nullptr, bad);
+        TGNN_CUDA(cudaGetLastError());
+        const int key_bits = bits_of(nodes * nodes - 1);
+        TGNN_TRY(radix_sort(s, n, key_bits, want_order, a->exec, &where));
+        if (a->itype_out == TGNN_I32)
+            gb::columns_from_keys_kernel<int32_t><<<grid, 256, 0, stream>>>(s.keys[where], n, nodes,
+                                                                           static_cast<int32_t *>(a->indices));
+        else
+            gb::columns_from_keys_kernel<int64_t><<<grid, 256, 0, stream>>>(s.keys[where], n, nodes,
+                                                                           static_cast<int64_t *>(a->indices));
+        TGNN_CUDA(cudaGetLastError());
+        if (want_order) {
+            gb::copy_ids_kernel<int32_t><<<grid, 256, 0, stream>>>(s.vals[where], n, a->edge_order);
+            TGNN_CUDA(cudaGetLastError());
+        }
+    }
+    const int pgrid = grid_for(a->num_nodes + 1, a->exec.device);
+    if (a->itype_out == TGNN_I32)
+        gb::indptr_from_keys_kernel<int32_t><<<pgrid, 256, 0, stream>>>(s.keys[where], n, nodes,
+                                                                       static_cast<int32_t *>(a->indptr));
+    else
+        gb::indptr_from_keys_kernel<int64_t><<<pgrid, 256, 0, stream>>>(s.keys[where], n, nodes,
+                                                                       static_cast<int64_t *>(a->indptr));
+    TGNN_CUDA(cudaGetLastError());
+    return TGNN_OK;
+}
+
+extern "C" int32_t tgnn_degree_order_stats(const tgnn_degree_order_stats_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));
+    TGNN_TRY(check_itype(a->itype, "indptr"));
+    TGNN_REQUIRE(a->num_rows > 0 && a->num_rows <= kMaxItems, TGNN_ERR_UNSUPPORTED, "num_rows %lld outside [1, 2^31)",
+                 static_cast<long long>(a->num_rows));
+    TGNN_REQUIRE(a->indptr != nullptr && a->out != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null pointer");
+    TGNN_REQUIRE(a->k_lo >= 0 && a->k_lo <= a->k_hi && a->k_hi < a->num_rows, TGNN_ERR_INVALID_ARGUMENT,
+                 "ranks %lld, %lld outside [0, %lld)", static_cast<long long>(a->k_lo), static_cast<long long>(a->k_hi),
+                 static_cast<long long>(a->num_rows));
+    TGNN_TRY(check_scratch(a->workspace, a->workspace_bytes, a->num_rows));
+    cudaStream_t stream = static_cast<cudaStream_t>(a->exec.stream);
+    const SortScratch s = carve(a->workspace, a->num_rows);
+    const int grid = grid_for(a->num_rows, a->exec.device);
+    if (a->itype == TGNN_I32)
+        gb::degree_keys_kernel<int32_t><<<grid, 256, 0, stream>>>(static_cast<const int32_t *>(a->indptr), a->num_rows, 0,
+                                                                 0.0f, s.keys[0], nullptr);
+    else
+        gb::degree_keys_kernel<int64_t><<<grid, 256, 0, stream>>>(static_cast<const int64_t *>(a->indptr), a->num_rows, 0,
+                                                                 0.0f, s.keys[0], nullptr);
+    TGNN_CUDA(cudaGetLastError());
+    int where = 0;
+    TGNN_TRY(radix_sort(s, a->num_rows, 32, false, a->exec, &where));  // a degree is below 2^31
+    gb::pick_order_stats_kernel<<<1, 32, 0, stream>>>(s.keys[where], a->num_rows, a->k_lo, a->k_hi, a->out);
+    TGNN_CUDA(cudaGetLastError());
+    return TGNN_OK;
+}
+
+extern "C" int32_t tgnn_partition_rows(const tgnn_partition_rows_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));
+    TGNN_TRY(check_itype(a->itype, "indptr"));
+    TGNN_REQUIRE(a->num_rows > 0 && a->num_rows <= kMaxItems, TGNN_ERR_UNSUPPORTED, "num_rows %lld outside [1, 2^31)",
+                 static_cast<long long>(a->num_rows));
+    TGNN_REQUIRE(a->indptr != nullptr && a->rows_out != nullptr && a->num_light != nullptr, TGNN_ERR_INVALID_ARGUMENT,
+                 "null pointer");
+    TGNN_TRY(check_scratch(a->workspace, a->workspace_bytes, a->num_rows));
+    cudaStream_t stream = static_cast<cudaStream_t>(a->exec.stream);
+    const SortScratch s = carve(a->workspace, a->num_rows);
+    const int grid = grid_for(a->num_rows, a->exec.device);
+    if (a->itype == TGNN_I32)
+        gb::degree_keys_kernel<int32_t><<<grid, 256, 0, stream>>>(static_cast<const int32_t *>(a->indptr), a->num_rows, 1,
+                                                                 a->cut, s.keys[0], s.vals[0]);
+    else
+        gb::degree_keys_kernel<int64_t><<<grid, 256, 0, stream>>>(static_cast<const int64_t *>(a->indptr), a->num_rows, 1,
+                                                                 a->cut, s.keys[0], s.vals[0]);
+    TGNN_CUDA(cudaGetLastError());
+    int where = 0;
+    TGNN_TRY(radix_sort(s, a->num_rows, 1, true, a->exec, &where));
+    if (a->itype == TGNN_I32)
+        gb::copy_ids_kernel<int32_t><<<grid, 256, 0, stream>>>(s.vals[where], a->num_rows,
+                                                              static_cast<int32_t *>(a->rows_out));
+    else
+        gb::copy_ids_kernel<int64_t><<<grid, 256, 0, stream>>>(s.vals[where], a->num_rows,
+                                                              static_cast<int64_t *>(a->rows_out));
+    TGNN_CUDA(cudaGetLastError());
+    gb::count_zero_keys_kernel<<<1, 32, 0, stream>>>(s.keys[where], a->num_rows, a->num_light);
+    TGNN_CUDA(cudaGetLastError());
+    return TGNN_OK;
+}

@@ -90,7 +90,7 @@ extern "C" int32_t tgnn_gt_forward(const tgnn_gt_fwd_args *a) {
         p.ldo0 = a->out.row_stride;
         p.lse_out = a->lse;
         return run_tiers<GtFwdOp<T, I, decltype(vt)::value>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
-                                                             a->workspace_bytes, false);
+                                                             a->workspace_bytes, false, true);
     });
 }
 
@@ -121,7 +121,7 @@ extern "C" int32_t tgnn_gt_backward_dst(const tgnn_gt_bwd_dst_args *a) {
         p.out0 = static_cast<T *>(a->dk.data);
         p.ldo0 = a->dk.row_stride;
         return run_tiers<GtBwdDstOp<T, I, decltype(vt)::value>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
-                                                                a->workspace_bytes, false);
+                                                                a->workspace_bytes, false, true);
     });
 }
 
@@ -155,6 +155,6 @@ extern "C" int32_t tgnn_gt_backward_src(const tgnn_gt_bwd_src_args *a) {
         p.out1 = static_cast<T *>(a->dv.data);
         p.ldo1 = a->dv.row_stride;
         return run_tiers<GtBwdSrcOp<T, I, decltype(vt)::value>>(p, a->csr_t, a->sched, a->exec, geo, a->workspace,
-                                                                a->workspace_bytes, false);
+                                                                a->workspace_bytes, false, true);
     });
 }

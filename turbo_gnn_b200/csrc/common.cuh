@@ -150,6 +150,16 @@ __device__ __forceinline__ void st_stream16(void *p, const uint4 &v) {
                  : "memory");
 }
 
+// Single words that are written once and read once much later (parked row states): evict-first.
+__device__ __forceinline__ uint32_t ld_word_once(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.global.cs.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_word_once(uint32_t *p, uint32_t v) {
+    asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // 32-byte (256-bit) forms of the three accesses above; sm_100 has 256-bit global
 // loads and stores.  `p` must be 32-byte aligned.
 __device__ __forceinline__ void ld_gather32(const void *p, uint64_t policy, uint4 &lo, uint4 &hi) {

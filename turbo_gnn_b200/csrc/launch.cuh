@@ -92,18 +92,54 @@ int32_t check_attn_mat(const tgnn_mat &m, const char *name, int64_t rows, int64_
 
 template <class Op>
 size_t hub_scratch_bytes(int64_t num_chunks, int slices) {
-    return static_cast<size_t>(num_chunks) * slices * Op::kWords * 32 * sizeof(uint32_t);
+    const size_t raw = static_cast<size_t>(num_chunks) * slices * Op::kWords * 32 * sizeof(uint32_t);
+    return (raw + 255) / 256 * 256;
+}
+// Parked row states of a column-tiled call: one slot per row of the CSR.
+template <class Op>
+size_t tile_scratch_bytes(int64_t num_rows, int slices) {
+    const size_t raw = static_cast<size_t>(num_rows) * slices * Op::kWords * 32 * sizeof(uint32_t);
+    return (raw + 255) / 256 * 256;
 }
 
 // Runs `Op` over the light, heavy and hub tiers.  `persistent_light` caps the
 // light grid so that each warp visits many rows (ops with cross-row carry).
+// `tiled` = the op takes part in column tiling (tgnn_schedule.num_tiles).
 template <class Op>
 int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_schedule &s, const tgnn_exec &ex,
-                  const Geometry &geo, void *scratch, size_t scratch_bytes, bool persistent_light) {
+                  const Geometry &geo, void *scratch, size_t scratch_bytes, bool persistent_light,
+                  bool tiled = false) {
     using I = typename Op::index_t;
     cudaStream_t stream = static_cast<cudaStream_t>(ex.stream);
     CsrDev<I> c{static_cast<const I *>(csr.indptr), static_cast<const I *>(csr.indices)};
     const int carry_smem = Op::kCarryWords * 32 * static_cast<int>(sizeof(uint32_t));
+
+    // Scratch: hub partials first, then the parked row states of a tiled call.
+    const size_t hub_need = s.num_hub > 0 ? hub_scratch_bytes<Op>(s.num_chunks, geo.slices) : 0;
+    const int tiles = (tiled && s.num_tiles >= 2 && s.tile_ptr != nullptr) ? s.num_tiles : 1;
+    const size_t tile_need = tiles > 1 ? tile_scratch_bytes<Op>(csr.num_rows, geo.slices) : 0;
+    if (hub_need + tile_need > 0) {
+        TGNN_REQUIRE(scratch != nullptr && scratch_bytes >= hub_need + tile_need, TGNN_ERR_WORKSPACE,
+                     "the call needs %zu bytes of scratch (%zu hub tier + %zu column tiles), got %zu",
+                     hub_need + tile_need, hub_need, tile_need, scratch_bytes);
+        TGNN_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, TGNN_ERR_WORKSPACE,
+                     "scratch must be 256-byte aligned");
+    }
+    TGNN_REQUIRE(tiles <= 64, TGNN_ERR_LAUNCH_PARAM, "Wrong int value: %d column tiles, at most 64", tiles);
+    uint32_t *partials = static_cast<uint32_t *>(scratch);
+    uint32_t *parked = reinterpret_cast<uint32_t *>(static_cast<unsigned char *>(scratch) + hub_need);
+    const I *tile_ptr = static_cast<const I *>(s.tile_ptr);
+    auto tile_of = [&](int t) {
+        TileDev<I> td{nullptr, nullptr, nullptr, 1, 1};
+        if (tiles > 1) {
+            td.begin = tile_ptr + static_cast<size_t>(t) * csr.num_rows;
+            td.end = tile_ptr + static_cast<size_t>(t + 1) * csr.num_rows;
+            td.state = parked;
+            td.first = t == 0;
+            td.last = t == tiles - 1;
+        }
+        return td;
+    };
 
     // Heavy and hub rows have the long critical paths: they are launched first, on the side
     // stream when the call also has light rows, and the light tier fills the rest of the GPU.
@@ -114,57 +150,53 @@ int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_
     HubDev<I> hub{static_cast<const I *>(s.hub_rows), s.hub_part_ptr, s.chunk_hub, s.chunk_edges};
     const int hw = s.heavy_warps;
     const size_t merge_smem = static_cast<size_t>(hw > 1 ? hw - 1 : 0) * Op::kWords * 32 * sizeof(uint32_t);
-    if (s.num_hub > 0) {
-        const size_t need = hub_scratch_bytes<Op>(s.num_chunks, geo.slices);
-        TGNN_REQUIRE(scratch != nullptr && scratch_bytes >= need, TGNN_ERR_WORKSPACE,
-                     "hub tier needs %zu bytes of scratch, got %zu", need, scratch_bytes);
-        TGNN_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, TGNN_ERR_WORKSPACE,
-                     "scratch must be 256-byte aligned");
-        uint32_t *partials = static_cast<uint32_t *>(scratch);
+    if (s.num_hub > 0) {  // hub rows are edge-split already: one untiled pass
         dim3 grid(static_cast<unsigned>(s.num_chunks), geo.slices);
         auto k = sweep_heavy_kernel<Op, true>;
         if (merge_smem > 48 * 1024)
             TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
-        k<<<grid, hw * 32, merge_smem, big>>>(p, c, nullptr, hub, partials, geo.G);
+        k<<<grid, hw * 32, merge_smem, big>>>(p, c, nullptr, hub, partials, geo.G, TileDev<I>{nullptr, nullptr, nullptr, 1, 1});
         TGNN_CUDA(cudaGetLastError());
         dim3 mgrid(static_cast<unsigned>((s.num_hub + 3) / 4), geo.slices);
         hub_merge_kernel<Op><<<mgrid, 128, 0, big>>>(p, c, hub, s.num_hub, partials, geo.G);
         TGNN_CUDA(cudaGetLastError());
     }
-    if (s.num_heavy > 0) {
-        dim3 grid(static_cast<unsigned>(s.num_heavy), geo.slices);
-        auto k = sweep_heavy_kernel<Op, false>;
-        if (merge_smem > 48 * 1024)
-            TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
-        k<<<grid, hw * 32, merge_smem, big>>>(p, c, static_cast<const I *>(s.heavy_rows), hub, nullptr, geo.G);
-        TGNN_CUDA(cudaGetLastError());
-    }
-
     HubDev<I> no_hub{nullptr, nullptr, nullptr, 0};
-    if (s.num_light > 0 && s.light_warps_per_row > 1) {
-        // Light rows as CTA-per-row with a small CTA (the reference's "warps per light row").
-        const int lw = s.light_warps_per_row;
-        const size_t smem = static_cast<size_t>(lw - 1) * Op::kWords * 32 * sizeof(uint32_t);
-        dim3 grid(static_cast<unsigned>(s.num_light), geo.slices);
-        auto k = sweep_heavy_kernel<Op, false>;
-        if (smem > 48 * 1024)
-            TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<grid, lw * 32, smem, stream>>>(p, c, static_cast<const I *>(s.light_rows), no_hub, nullptr, geo.G);
-        TGNN_CUDA(cudaGetLastError());
-    } else if (s.num_light > 0) {
-        const int warps = s.light_warps;
-        TGNN_REQUIRE(warps * 32 <= Op::kLightMaxThreads, TGNN_ERR_LAUNCH_PARAM,
-                     "Wrong int value: %d light warps per CTA, this op takes at most %d", warps,
-                     Op::kLightMaxThreads / 32);
-        int64_t blocks = (s.num_light + warps - 1) / warps;
-        if (persistent_light) {
-            const int64_t cap = static_cast<int64_t>(sm_count(ex.device)) * (2048 / (warps * 32)) ;
-            if (blocks > cap) blocks = cap;
+    for (int t = 0; t < tiles; ++t) {
+        const TileDev<I> td = tile_of(t);
+        if (s.num_heavy > 0) {
+            dim3 grid(static_cast<unsigned>(s.num_heavy), geo.slices);
+            auto k = sweep_heavy_kernel<Op, false>;
+            if (merge_smem > 48 * 1024)
+                TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem));
+            k<<<grid, hw * 32, merge_smem, big>>>(p, c, static_cast<const I *>(s.heavy_rows), hub, nullptr, geo.G, td);
+            TGNN_CUDA(cudaGetLastError());
         }
-        dim3 grid(static_cast<unsigned>(blocks), geo.slices);
-        sweep_light_kernel<Op><<<grid, warps * 32, carry_smem * warps, stream>>>(
-            p, c, static_cast<const I *>(s.light_rows), s.num_light, geo.G);
-        TGNN_CUDA(cudaGetLastError());
+        if (s.num_light > 0 && s.light_warps_per_row > 1) {
+            // Light rows as CTA-per-row with a small CTA (the reference's "warps per light row").
+            const int lw = s.light_warps_per_row;
+            const size_t smem = static_cast<size_t>(lw - 1) * Op::kWords * 32 * sizeof(uint32_t);
+            dim3 grid(static_cast<unsigned>(s.num_light), geo.slices);
+            auto k = sweep_heavy_kernel<Op, false>;
+            if (smem > 48 * 1024)
+                TGNN_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            k<<<grid, lw * 32, smem, stream>>>(p, c, static_cast<const I *>(s.light_rows), no_hub, nullptr, geo.G, td);
+            TGNN_CUDA(cudaGetLastError());
+        } else if (s.num_light > 0) {
+            const int warps = s.light_warps;
+            TGNN_REQUIRE(warps * 32 <= Op::kLightMaxThreads, TGNN_ERR_LAUNCH_PARAM,
+                         "Wrong int value: %d light warps per CTA, this op takes at most %d", warps,
+                         Op::kLightMaxThreads / 32);
+            int64_t blocks = (s.num_light + warps - 1) / warps;
+            if (persistent_light) {
+                const int64_t cap = static_cast<int64_t>(sm_count(ex.device)) * (2048 / (warps * 32));
+                if (blocks > cap) blocks = cap;
+            }
+            dim3 grid(static_cast<unsigned>(blocks), geo.slices);
+            sweep_light_kernel<Op><<<grid, warps * 32, carry_smem * warps, stream>>>(
+                p, c, static_cast<const I *>(s.light_rows), s.num_light, geo.G, td);
+            TGNN_CUDA(cudaGetLastError());
+        }
     }
     TGNN_TRY(fork.join());
     return TGNN_OK;

@@ -39,6 +39,21 @@ struct HubDev {
     int32_t chunk_edges;
 };
 
+// Column tiling.  A sweep may be cut into passes over column ranges ("tiles"): pass t of a row
+// folds the edges [begin[row], end[row]) (the row's edges whose column lies in tile t; columns
+// are sorted inside a row, so this is a contiguous piece of the row) and the row's state
+// travels from pass to pass through `state` ([row][slice][word][lane] words).  All rows sweep
+// the same column range at the same time, which keeps the gathered rows of that range in L2.
+// begin == nullptr: one pass over the whole row, no state traffic.
+template <typename I>
+struct TileDev {
+    const I *begin;
+    const I *end;
+    uint32_t *state;
+    int first;  // no state to pick up
+    int last;   // finish the row instead of parking its state
+};
+
 struct Lanes {
     int lane;    // 0..31
     int G;       // lanes per edge group (power of two)
@@ -119,11 +134,36 @@ __device__ __forceinline__ void merge_groups(Op &op, typename Op::State &st, con
     }
 }
 
+// ---- state parking between column tiles ---------------------------------------------------
+template <class Op>
+__device__ __forceinline__ uint32_t *tile_slot(uint32_t *state, int64_t row) {
+    return state + (static_cast<size_t>(row) * gridDim.y + blockIdx.y) * Op::kWords * 32;
+}
+
+// Adds the state parked by the previous pass (every lane owns one column of the slot).
+template <class Op>
+__device__ __forceinline__ void tile_pick_up(Op &op, typename Op::State &st, const uint32_t *slot, int lane) {
+    uint32_t w[Op::kWords];
+#pragma unroll
+    for (int i = 0; i < Op::kWords; ++i) w[i] = ld_word_once(slot + i * 32 + lane);
+    typename Op::State parked;
+    op.from_words(parked, w);
+    op.merge(st, parked);
+}
+
+template <class Op>
+__device__ __forceinline__ void tile_park(Op &op, const typename Op::State &st, uint32_t *slot, int lane) {
+    uint32_t w[Op::kWords];
+    op.to_words(st, w);
+#pragma unroll
+    for (int i = 0; i < Op::kWords; ++i) st_word_once(slot + i * 32 + lane, w[i]);
+}
+
 // ---- light tier ---------------------------------------------------------------
 template <class Op>
 __global__ void __launch_bounds__(Op::kLightMaxThreads, Op::kLightMinBlocks) sweep_light_kernel(typename Op::Params p, CsrDev<typename Op::index_t> csr,
                                                           const typename Op::index_t *__restrict__ rows,
-                                                          int64_t n_rows, int G) {
+                                                          int64_t n_rows, int G, TileDev<typename Op::index_t> tile) {
     using I = typename Op::index_t;
     extern __shared__ __align__(16) uint32_t smem[];
     const Lanes L = make_lanes(G);
@@ -135,14 +175,32 @@ __global__ void __launch_bounds__(Op::kLightMaxThreads, Op::kLightMinBlocks) swe
     for (int64_t r = static_cast<int64_t>(blockIdx.x) * warps + warp; r < n_rows;
          r += static_cast<int64_t>(gridDim.x) * warps) {
         const I row = rows[r];
-        const I e0 = csr.indptr[row];
-        const I e1 = csr.indptr[row + 1];
+        I e0, e1;
+        if (tile.begin != nullptr) {
+            e0 = tile.begin[row];
+            e1 = tile.end[row];
+            // a row with nothing in this tile keeps the state it parked earlier
+            if (e0 == e1 && !tile.first && !tile.last) continue;
+        } else {
+            e0 = csr.indptr[row];
+            e1 = csr.indptr[row + 1];
+        }
         typename Op::Row rc;
         op.row_begin(row, rc);
         typename Op::State st;
         op.init(st);
         sweep_edges(op, rc, st, csr.indices, e0, e1, 0, 1, L);
         merge_groups(op, st, L);
+        if (tile.begin != nullptr) {
+            uint32_t *slot = tile_slot<Op>(tile.state, row);
+            if (!tile.first) tile_pick_up(op, st, slot, L.lane);
+            if (!tile.last) {
+                tile_park(op, st, slot, L.lane);
+                continue;
+            }
+            e0 = csr.indptr[row];
+            e1 = csr.indptr[row + 1];
+        }
         op.row_end(row, rc, st, e1 - e0);
         op.carry_add(carry, st);
     }
@@ -157,7 +215,7 @@ template <class Op, bool kPartial>
 __global__ void __launch_bounds__(512)
     sweep_heavy_kernel(typename Op::Params p, CsrDev<typename Op::index_t> csr,
                        const typename Op::index_t *__restrict__ rows, HubDev<typename Op::index_t> hub,
-                       uint32_t *__restrict__ partials, int G) {
+                       uint32_t *__restrict__ partials, int G, TileDev<typename Op::index_t> tile) {
     using I = typename Op::index_t;
     extern __shared__ __align__(16) uint32_t smem[];
     const Lanes L = make_lanes(G);
@@ -175,8 +233,14 @@ __global__ void __launch_bounds__(512)
         if (e1 > re) e1 = re;
     } else {
         row = rows[blockIdx.x];
-        e0 = csr.indptr[row];
-        e1 = csr.indptr[row + 1];
+        if (tile.begin != nullptr) {
+            e0 = tile.begin[row];
+            e1 = tile.end[row];
+            if (e0 == e1 && !tile.first && !tile.last) return;  // CTA-uniform: the parked state stands
+        } else {
+            e0 = csr.indptr[row];
+            e1 = csr.indptr[row + 1];
+        }
     }
     Op op(p, L);
     typename Op::Row rc;
@@ -211,6 +275,16 @@ __global__ void __launch_bounds__(512)
 #pragma unroll
             for (int i = 0; i < Op::kWords; ++i) dst[i * 32 + L.lane] = w[i];
         } else {
+            if (tile.begin != nullptr) {
+                uint32_t *slot = tile_slot<Op>(tile.state, row);
+                if (!tile.first) tile_pick_up(op, st, slot, L.lane);
+                if (!tile.last) {
+                    tile_park(op, st, slot, L.lane);
+                    return;
+                }
+                e0 = csr.indptr[row];
+                e1 = csr.indptr[row + 1];
+            }
             op.row_end(row, rc, st, e1 - e0);
             op.flush_row(st);
         }

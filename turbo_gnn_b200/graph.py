@@ -214,15 +214,22 @@ class AdjacencyForwardBackwardWithNodeBuckets:
             if index_dtype is not None:
                 bwd_indptr, bwd_indices = bwd_indptr.to(index_dtype), bwd_indices.to(index_dtype)
         idx_dt = index_dtype or fwd_indptr.dtype
-        if fwd_counts is None:
-            fwd_counts = _row_degrees(fwd_indptr)
-        fwd_light, fwd_heavy = _bucket_nodes_by_degree(fwd_counts, quantile, index_dtype=idx_dt)
+
+        def bucket(indptr, counts):
+            if indptr.is_cuda and indptr.numel() > 1:  # the library's own selection + partition kernels
+                from . import graph_build
+
+                light, heavy, _ = graph_build.bucket_rows(indptr, quantile, index_dtype=idx_dt)
+                return light, heavy
+            if counts is None:
+                counts = _row_degrees(indptr)
+            return _bucket_nodes_by_degree(counts, quantile, index_dtype=idx_dt)
+
+        fwd_light, fwd_heavy = bucket(fwd_indptr, fwd_counts)
         if is_directed is False:
             bwd_light, bwd_heavy = fwd_light, fwd_heavy
         else:
-            if bwd_counts is None:
-                bwd_counts = _row_degrees(bwd_indptr)
-            bwd_light, bwd_heavy = _bucket_nodes_by_degree(bwd_counts, quantile, index_dtype=idx_dt)
+            bwd_light, bwd_heavy = bucket(bwd_indptr, bwd_counts)
         return cls(
             forward_indptr=fwd_indptr,
             forward_indices=fwd_indices,
@@ -246,8 +253,26 @@ class AdjacencyForwardBackwardWithNodeBuckets:
     ) -> "AdjacencyForwardBackwardWithNodeBuckets":
         """Build both CSRs from a COO ``edge_index`` of shape [2, E] (row 0 = source, row 1 = destination).
 
-        ``is_directed=False`` skips the backward CSR and aliases it to the forward one.
+        ``is_directed=False`` skips the backward CSR and aliases it to the forward one.  An edge
+        list on a CUDA device is sorted and bucketed by the library's own kernels
+        (:mod:`turbo_gnn_b200.graph_build`), a host edge list by the torch ops below; the arrays
+        are the same either way.
         """
+        if edge_index.is_cuda:
+            from . import graph_build
+
+            out_dt = index_dtype or torch.int64
+            src, dst = edge_index[0], edge_index[1]
+
+            def csr(rows, cols):
+                ptr, idx, _ = graph_build.coo_to_csr(rows, cols, num_nodes, out_dt)
+                if index_dtype is None and idx.dtype != edge_index.dtype:
+                    idx = idx.to(edge_index.dtype)  # the torch path keeps the edge list's dtype here
+                return ptr, idx
+
+            fwd = csr(dst, src)
+            bwd = csr(src, dst) if is_directed is not False else None
+            return cls._assemble(fwd, bwd, None, None, quantile, index_dtype, is_directed)
         f_ptr, f_idx, _, f_counts = build_csr_as_is(edge_index, None, num_nodes, do_transpose=True)
         bwd, b_counts = None, None
         if is_directed is not False:
