@@ -158,3 +158,85 @@ def test_kernel_classes_expose_reference_attribute_names():
     assert (t.forward_light_warps, t.forward_heavy_warps, t.backward_light_warps) == (4, 8, 1)
     assert {p.name for p in t.get_tunable_backward_graph_params()} == {"backward_huge_degree_threshold_quantile"}
     assert ReductionAggrKernel._get_or_create(reduce="min") is not ReductionAggrKernel._get_or_create(reduce="max")
+
+
+# ---- search strategies (host logic) ---------------------------------------------------------------
+
+
+def _objective(cfg):
+    # separable with one interaction; unique minimum at a=3, b="x", c=16, d=2
+    return abs(cfg["a"] - 3) * 2.0 + (0.0 if cfg["b"] == "x" else 1.5) + abs(cfg["c"] - 16) / 8 + (cfg["d"] - 2) ** 2 \
+        + (0.7 if (cfg["a"] == 3 and cfg["b"] == "y") else 0.0)
+
+
+_SPACE = {"a": [0, 1, 2, 3, 4, 5], "b": ["x", "y", "z"], "c": [1, 2, 4, 8, 16, 32], "d": [0, 1, 2, 3, 4]}
+
+
+def test_grid_search_visits_every_combination_once():
+    from turbo_gnn_b200._search import GridSearch
+
+    grid = GridSearch(_SPACE)
+    seen = []
+    while (cfg := grid.ask()) is not None:
+        seen.append(tuple(cfg.values()))
+        grid.tell(cfg, _objective(cfg))
+    assert grid.size == 6 * 3 * 6 * 5 == len(seen) == len(set(seen))
+    assert grid.best()[0] == {"a": 3, "b": "x", "c": 16, "d": 2}
+
+
+def test_tpe_finds_the_optimum_in_a_fraction_of_the_grid_and_is_reproducible():
+    from turbo_gnn_b200._search import TPESearch
+
+    def run(seed):
+        tpe = TPESearch(_SPACE, seed=seed, n_startup=10)
+        asked = []
+        for _ in range(120):  # grid: 540
+            cfg = tpe.ask()
+            assert cfg is not None
+            asked.append(tuple(cfg.values()))
+            tpe.tell(cfg, _objective(cfg) if cfg["d"] != 4 else float("inf"))  # d=4: an invalid launch parameter
+        assert len(set(asked)) == len(asked)  # never the same combination twice
+        return asked, tpe.best()
+
+    asked, best = run(0)
+    assert best[1] <= 0.5 and best[0]["a"] == 3 and best[0]["b"] == "x"
+    assert run(0)[0] == asked  # same seed, same trajectory
+    hits = sum(run(s)[1][1] == 0.0 for s in range(5))
+    assert hits >= 3  # the exact optimum in most runs with 22 % of the grid
+
+
+def test_tpe_exhausts_small_spaces_and_then_stops():
+    from turbo_gnn_b200._search import TPESearch, make_search
+
+    tpe = TPESearch({"p": [1, 2], "q": ["a", "b", "c"]}, seed=1, n_startup=2)
+    got = []
+    while (cfg := tpe.ask()) is not None:
+        got.append((cfg["p"], cfg["q"]))
+        tpe.tell(cfg, float(cfg["p"]))
+    assert sorted(got) == [(p, q) for p in (1, 2) for q in "abc"]
+    assert type(make_search("tpe", {"p": [1, 2]}, max_trials=8)).__name__ == "GridSearch"  # budget covers the grid
+    assert type(make_search("tpe", _SPACE, max_trials=50)).__name__ == "TPESearch"
+    with pytest.raises(ValueError):
+        make_search("anneal", _SPACE, max_trials=5)
+
+
+def test_autotune_with_tpe_budget_and_trial_records(tmp_path):
+    graph = make_graph(random_edges(60, 500, 3), 60, device="cpu")
+    kern = Doubler()
+    x = torch.ones(60, 8)
+    cfg = AutotuneConfig(warmup=0, iters=1, cache_dir=str(tmp_path), search="tpe", max_trials=5, seed=3)
+    with patch("turbo_gnn_b200._autotune._timer.time_callable", scripted_timer(kern)):
+        kern._inline_autotune(x, graph, cfg)
+    records = list((tmp_path / "trials").glob("*.json"))
+    assert len(records) == 5  # one JSON record per timed trial, failures included
+    timed = len(kern.calls)
+    # a second search with the same seed replays the records instead of timing again
+    kern2 = Doubler()
+    with patch("turbo_gnn_b200._autotune._timer.time_callable", scripted_timer(kern2)):
+        import os
+
+        for f in tmp_path.glob("Doubler_*.json"):
+            os.remove(f)  # drop the winner file so that the search itself runs again
+        kern2._inline_autotune(x, graph, cfg)
+    assert len(kern2.calls) == 0 and timed >= 4
+    assert kern2.speed == kern.speed

@@ -28,7 +28,7 @@ from typing import Any, Callable, ClassVar
 
 import torch
 
-from . import _timer
+from . import _search, _timer
 
 logger = logging.getLogger(__name__)
 
@@ -44,13 +44,17 @@ class TunableParam:
 
 @dataclass
 class AutotuneConfig:
-    """How a search is timed (``warmup``/``iters`` per candidate) and whether results persist on disk."""
+    """How a search is timed (``warmup``/``iters`` per candidate), which combinations it visits and
+    whether results persist on disk (the winner per problem, and one record per timed trial)."""
 
     warmup: int = 10
     iters: int = 50
     tune_backward: bool = False
     cache_dir: str | None = None
     use_cache: bool = True
+    search: str = "grid"  # "grid": every combination; "tpe": at most max_trials, picked by a Parzen estimator
+    max_trials: int | None = None
+    seed: int = 0
 
 
 def _build_combinations(params: list[TunableParam]) -> list[dict[str, Any]]:
@@ -215,7 +219,8 @@ class TunableKernel(ABC):
             json.dump({"kernel": self.name, "graph_config": graph_cfg, "kernel_config": kernel_cfg, "ms": ms}, fh)
 
     def _inline_autotune(self, x, graph_repr, config=None, **kwargs):
-        """Time every (graph axes) x (kernel axes) combination; return the fastest as a result dict.
+        """Time (graph axes) x (kernel axes) combinations -- all of them, or ``max_trials`` chosen by
+        the TPE search -- and return the fastest as a result dict.
 
         A combination whose run raises ``RuntimeError`` (a launch parameter the library rejects)
         is skipped.  The winning kernel attributes stay configured on return.
@@ -231,13 +236,31 @@ class TunableKernel(ABC):
             return from_disk
 
         best_ms, best, best_graph_cfg = float("inf"), untouched, {}
+        graph_names = {p.name for p in graph_axes}
+        search = _search.make_search(config.search, {p.name: list(p.values) for p in graph_axes + kernel_axes},
+                                     config.max_trials, config.seed)
+        trials = _search.TrialCache(config.cache_dir if config.use_cache else None)
+        gpu = torch.cuda.get_device_name(x.device) if getattr(x, "is_cuda", False) else "cpu"
+        shape = (_feature_width(x), graph_repr.forward_indptr.numel() - 1, graph_repr.forward_indices.numel())
+        graphs: dict[tuple, Any] = {}
         self._is_autotuning = True
         try:
-            for graph_cfg in _build_combinations(graph_axes):
-                candidate_graph = graph_repr.repartition(**graph_cfg) if graph_cfg else graph_repr
-                for kernel_cfg in _build_combinations(kernel_axes):
-                    if kernel_cfg:
-                        self.configure(**kernel_cfg)
+            budget = config.max_trials if config.max_trials is not None else search.size
+            for _ in range(budget):
+                cfg = search.ask()
+                if cfg is None:
+                    break
+                graph_cfg = {k: v for k, v in cfg.items() if k in graph_names}
+                kernel_cfg = {k: v for k, v in cfg.items() if k not in graph_names}
+                gkey = tuple(sorted((k, repr(v)) for k, v in graph_cfg.items()))
+                if gkey not in graphs:
+                    graphs[gkey] = graph_repr.repartition(**graph_cfg) if graph_cfg else graph_repr
+                candidate_graph = graphs[gkey]
+                if kernel_cfg:
+                    self.configure(**kernel_cfg)
+                key = _search.trial_key(self.name + (":bwd" if config.tune_backward else ""), *shape, gpu, cfg)
+                ms = trials.load(key)
+                if ms is None:
                     try:
                         fn = (self.make_backward_bench_fn if config.tune_backward else self.make_forward_bench_fn)(
                             x, candidate_graph, **kwargs
@@ -245,10 +268,12 @@ class TunableKernel(ABC):
                         ms = _timer.time_callable(fn, warmup=config.warmup, iters=config.iters).ms_per_iter
                     except RuntimeError:
                         logger.debug("Skipping invalid config: graph=%s kernel=%s", graph_cfg, kernel_cfg)
-                        continue
-                    if ms < best_ms:
-                        best_ms, best_graph_cfg = ms, graph_cfg
-                        best = {"kernel_config": kernel_cfg, "graph_repr": candidate_graph}
+                        ms = float("inf")
+                    trials.store(key, {"kernel": self.name, "config": {k: repr(v) for k, v in cfg.items()}}, ms)
+                search.tell(cfg, ms)
+                if ms < best_ms:
+                    best_ms, best_graph_cfg = ms, graph_cfg
+                    best = {"kernel_config": kernel_cfg, "graph_repr": candidate_graph}
         finally:
             self._is_autotuning = False
         if best["kernel_config"]:

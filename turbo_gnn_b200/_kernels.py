@@ -30,15 +30,18 @@ class _HubTunables:
 
     hub_chunk_edges = None  # None: derived from the graph
     hub_min_degree = None
+    column_tiles = None
 
     def _hub(self):
-        return _C.hub_tier(chunk_edges=self.hub_chunk_edges, hub_min_degree=self.hub_min_degree)
+        return _C.hub_tier(chunk_edges=self.hub_chunk_edges, hub_min_degree=self.hub_min_degree,
+                           column_tiles=self.column_tiles)
 
     @staticmethod
     def _hub_axes() -> list[TunableParam]:
         return [
             TunableParam("hub_chunk_edges", [None, 2048], default=None),
             TunableParam("hub_min_degree", [None, 4096], default=None),
+            TunableParam("column_tiles", [None, 1], default=None),
         ]
 
 
