@@ -112,6 +112,15 @@ def _chunk_elems(dt: torch.dtype) -> int:
     return 4 if dt == torch.float32 else 8
 
 
+def _feature_cols(feat: int, dt: torch.dtype) -> int:
+    """Row width the reduction kernels work on: the feature count rounded up to whole 16-byte
+    chunks, and to 32 bytes once a row has more than one chunk (the kernels then use 256-bit
+    accesses)."""
+    chunk = _chunk_elems(dt)
+    cols = _round_up(max(feat, 1), chunk)
+    return cols if cols == chunk else _round_up(cols, 2 * chunk)
+
+
 def _rows_ok(t: torch.Tensor, align: int = 16) -> bool:
     """True when `t` ([N,F] or [N,H,D]) can be read with `align`-byte row accesses as is."""
     esz = t.element_size()
@@ -186,8 +195,8 @@ def reduction_aggr_forward_partitioned(
     n_rows = edge_ptr.numel() - 1
     feat = X.shape[1]
     minmax = reduce in ("min", "max")
-    cols = _round_up(max(feat, 1), _chunk_elems(X.dtype))
-    x_in = _as_rows(_pad_cols(X, cols))
+    cols = _feature_cols(feat, X.dtype)
+    x_in = _as_rows(_pad_cols(X, cols), 32)
     out = torch.empty((n_rows, cols), dtype=X.dtype, device=X.device)
     arg = None
     if minmax and want_arg:
@@ -225,7 +234,7 @@ def reduction_aggr_backward(grad_out, arg_idx, num_src_nodes, warps_per_block=8)
     if arg_idx.shape != grad_out.shape:
         raise RuntimeError("arg_idx and grad_out shapes must match")
     feat = grad_out.shape[1]
-    cols = _round_up(max(feat, 1), _chunk_elems(grad_out.dtype))
+    cols = _feature_cols(feat, grad_out.dtype)
     g_in = _as_rows(_pad_cols(grad_out, cols))
     a_in = arg_idx.contiguous() if cols == feat else F.pad(arg_idx, (0, cols - feat), value=-1).contiguous()
     grad_x = torch.empty((int(num_src_nodes), cols), dtype=grad_out.dtype, device=grad_out.device)
@@ -362,8 +371,8 @@ def csr_SPMM_normalized(
             raise RuntimeError("do_transpose_a expects features with one row per CSR row")
     g = _spmm_graph(indptr, indices, num_cols, use_cache)
     feat = features.shape[1]
-    cols = _round_up(max(feat, 1), _chunk_elems(features.dtype))
-    x_in = _as_rows(_pad_cols(features, cols))
+    cols = _feature_cols(feat, features.dtype)
+    x_in = _as_rows(_pad_cols(features, cols), 32)
     has_w = edge_weights is not None and edge_weights.numel() > 0
     row_scale = col_scale = None
     if norm != "none":
@@ -816,8 +825,8 @@ def spmm_rows(indptr, indices, x, light_nodes, heavy_nodes, row_scale=None, col_
     _check_index_family(indptr, indices, light_nodes, heavy_nodes)
     n_rows = indptr.numel() - 1
     feat = x.shape[1]
-    cols = _round_up(max(feat, 1), _chunk_elems(x.dtype))
-    x_in = _as_rows(_pad_cols(x, cols))
+    cols = _feature_cols(feat, x.dtype)
+    x_in = _as_rows(_pad_cols(x, cols), 32)
     out = torch.empty((n_rows, cols), dtype=x.dtype, device=x.device)
     if n_rows > 0:
         sched = _sched(indptr, light_nodes, heavy_nodes, slots=_schedule.REDUCE_WARP_SLOTS)

@@ -151,21 +151,40 @@ int32_t check_mat(const tgnn_mat &m, const char *name, int64_t rows, int64_t col
     return TGNN_OK;
 }
 
-Geometry make_geometry(int64_t cols, int chunk_elems, int min_group_lanes) {
+Geometry make_geometry(int64_t cols, int chunk_elems, int min_group_lanes, bool wide_ok) {
     const int64_t chunks = (cols + chunk_elems - 1) / chunk_elems;
     Geometry g;
     g.slices = 1;
-    if (chunks <= 32) {
+    if (!wide_ok || chunks <= 32) {
+        // 16-byte accesses, one chunk per lane: rows of up to 32 chunks (a 512-byte row keeps the
+        // whole warp on one edge; two edges per warp with 32-byte accesses measured 20 % slower on
+        // a graph of short rows, where the per-row merge of the two halves dominates), and rows
+        // that cannot be addressed in 32-byte units, which go to feature slices when wider
         g.vpl = 1;
-        g.G = ilog2_ceil_pow2(static_cast<int>(chunks));
-        if (g.G < min_group_lanes) g.G = min_group_lanes;
-        if (g.G > 32) g.G = 32;
+        if (chunks <= 32) {
+            g.G = ilog2_ceil_pow2(static_cast<int>(chunks));
+        } else {
+            g.G = 32;
+            g.slices = static_cast<int>((chunks + 31) / 32);
+        }
+    } else if (chunks <= 64) {
+        // 32-byte accesses: a lane owns two consecutive chunks
+        g.vpl = 2;
+        g.G = ilog2_ceil_pow2(static_cast<int>((chunks + 1) / 2));
     } else {
         g.G = 32;
-        g.vpl = chunks <= 64 ? 2 : (chunks <= 128 ? 4 : 8);
-        g.slices = static_cast<int>((chunks + 255) / 256);
+        g.vpl = chunks <= 128 ? 4 : 8;
+        g.slices = static_cast<int>((chunks + 32 * g.vpl - 1) / (32 * g.vpl));
     }
+    if (g.G < min_group_lanes) g.G = min_group_lanes;
+    if (g.G > 32) g.G = 32;
     return g;
+}
+
+bool wide_rows_ok(const tgnn_mat &m) {
+    const size_t esz = dtype_size(m.dtype);
+    const int64_t pair = 32 / static_cast<int64_t>(esz);
+    return (reinterpret_cast<uintptr_t>(m.data) & 31u) == 0 && (m.row_stride * esz) % 32 == 0 && m.cols % pair == 0;
 }
 
 Geometry make_attn_geometry(int64_t cols, int head_dim, int32_t dtype) {

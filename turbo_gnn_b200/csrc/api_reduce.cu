@@ -102,10 +102,16 @@ int grid_for(int64_t work_items, int threads, int device) {
 
 size_t reduce_scratch_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_chunks, int64_t cols) {
     const int per = dtype == TGNN_F32 ? 4 : 8;
-    const Geometry geo = make_geometry(cols, per, 1);
-    size_t words = static_cast<size_t>(geo.vpl) * per;
-    if (op == TGNN_OP_REDUCE_MINMAX) words *= (1 + itype_size(itype) / 4);
-    return static_cast<size_t>(num_chunks) * geo.slices * words * 32 * sizeof(uint32_t);
+    // the larger of the two geometries a call may end up with (32-byte or 16-byte row access)
+    size_t worst = 0;
+    for (int wide = 0; wide < 2; ++wide) {
+        const Geometry geo = make_geometry(cols, per, 1, wide != 0);
+        size_t words = static_cast<size_t>(geo.vpl) * per;
+        if (op == TGNN_OP_REDUCE_MINMAX) words *= (1 + itype_size(itype) / 4);
+        const size_t need = static_cast<size_t>(num_chunks) * geo.slices * words * 32 * sizeof(uint32_t);
+        if (need > worst) worst = need;
+    }
+    return worst;
 }
 
 }  // namespace tgnn
@@ -122,7 +128,7 @@ extern "C" int32_t tgnn_segment_reduce_forward(const tgnn_segment_reduce_args *a
     if (minmax && a->arg_idx != nullptr)
         TGNN_REQUIRE(aligned16(a->arg_idx), TGNN_ERR_INVALID_ARGUMENT, "arg_idx is not 16-byte aligned");
     const int per = a->x.dtype == TGNN_F32 ? 4 : 8;
-    const Geometry geo = make_geometry(a->x.cols, per, 1);
+    const Geometry geo = make_geometry(a->x.cols, per, 1, wide_rows_ok(a->x) && wide_rows_ok(a->out));
     return dispatch_tiv(a->x.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
         using T = typename decltype(tt)::type;
         using I = typename decltype(it)::type;
@@ -211,7 +217,7 @@ extern "C" int32_t tgnn_spmm(const tgnn_spmm_args *a) {
     TGNN_TRY(check_reduce_io(a->exec, a->csr, a->sched, a->x, a->out));
     if (a->csr.num_rows == 0) return TGNN_OK;
     const int per = a->x.dtype == TGNN_F32 ? 4 : 8;
-    const Geometry geo = make_geometry(a->x.cols, per, 1);
+    const Geometry geo = make_geometry(a->x.cols, per, 1, wide_rows_ok(a->x) && wide_rows_ok(a->out));
     const bool weighted = a->row_scale != nullptr || a->col_scale != nullptr || a->edge_weight != nullptr;
     return dispatch_tiv(a->x.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
         using T = typename decltype(tt)::type;

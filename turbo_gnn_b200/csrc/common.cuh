@@ -32,16 +32,21 @@
 #ifndef TGNN_ATTN_UNROLL
 #define TGNN_ATTN_UNROLL(vpl) ((vpl) >= 4 ? 1 : 2)
 #endif
-// Unroll and occupancy of the reductions / SpMM (CTAs of up to 256 threads): 4 resident CTAs
-// (64 registers) beat the unconstrained build by 15 % on a 65 M-edge bf16 SpMM.
+// Unroll of the reductions / SpMM.  Their warp-per-row kernels (CTAs of up to 256 threads) are
+// compiled for as many resident CTAs as the row state and the gathered fragments leave room
+// for: 4 (64 registers) beat the unconstrained build by 15 % on a 65 M-edge bf16 SpMM, but an op
+// that keeps 64 accumulators per lane must not be squeezed into 64 registers.
 #ifndef TGNN_REDUCE_UNROLL
-#define TGNN_REDUCE_UNROLL(vpl) ((vpl) >= 4 ? 2 : 4)
-#endif
-#ifndef TGNN_REDUCE_MIN_BLOCKS
-#define TGNN_REDUCE_MIN_BLOCKS(vpl) 4
+#define TGNN_REDUCE_UNROLL(vpl) ((vpl) >= 2 ? 2 : 4)
 #endif
 
 namespace tgnn {
+
+// Resident 256-thread CTAs per SM for an op that needs `live_regs` registers of state and
+// fragments (about 28 more go to addresses, indices and loop control).
+constexpr int reduce_min_blocks(int live_regs) {
+    return live_regs + 28 <= 64 ? 4 : (live_regs + 28 <= 80 ? 3 : (live_regs + 28 <= 128 ? 2 : 1));
+}
 
 constexpr int kWarp = 32;
 constexpr unsigned kFull = 0xffffffffu;

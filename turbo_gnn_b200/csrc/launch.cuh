@@ -76,14 +76,18 @@ int32_t check_schedule(const tgnn_schedule &s, const tgnn_csr &c);
 // known, base and row pitch 16-byte aligned, cols a multiple of the chunk.
 int32_t check_mat(const tgnn_mat &m, const char *name, int64_t rows, int64_t cols, int32_t dtype);
 
-// Lane geometry for a feature row of `cols` elements of `chunk_elems` per
-// 16 bytes: chunks per lane (1,2,4,8), lanes per edge group and feature slices.
+// Lane geometry of the reductions for a feature row of `cols` elements, `chunk_elems` per
+// 16 bytes: chunks per lane (1,2,4,8; consecutive chunks), lanes per edge group and feature
+// slices.  `wide_ok` (rows addressable in 32-byte units, see wide_rows_ok) allows two or more
+// chunks per lane, which the ops read and write with 256-bit accesses.
 struct Geometry {
     int vpl;     // chunks per lane
     int G;       // lanes per edge group
     int slices;  // grid.y
 };
-Geometry make_geometry(int64_t cols, int chunk_elems, int min_group_lanes);
+Geometry make_geometry(int64_t cols, int chunk_elems, int min_group_lanes, bool wide_ok);
+// Base address and row pitch multiples of 32 bytes, column count a multiple of two chunks.
+bool wide_rows_ok(const tgnn_mat &m);
 // Geometry of the attention ops: every lane owns `vpl` consecutive chunks that lie
 // inside one head (vpl <= head_dim / chunk_elems); a lane group holds whole heads.
 Geometry make_attn_geometry(int64_t cols, int head_dim, int32_t dtype);

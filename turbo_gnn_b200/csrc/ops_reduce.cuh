@@ -6,19 +6,44 @@
 
 namespace tgnn {
 
-// Feature offset (in elements) of chunk v of this lane, or -1 when the chunk
-// lies beyond the row.
+// Feature offset (in elements) of chunk v of this lane, or -1 when the chunk lies beyond the
+// row.  A lane owns kVpl CONSECUTIVE chunks; with two or more the host side guarantees rows
+// addressable in 32-byte units and an even chunk count, and the ops move chunk pairs with
+// 256-bit accesses.
 template <int kVpl, int kPerChunk>
 struct ChunkMap {
     int off[kVpl];
     __device__ __forceinline__ ChunkMap(const Lanes &L, int cols) {
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            const int o = ((L.slice * kVpl + v) * L.G + L.g_lane) * kPerChunk;
+            const int o = ((L.slice * L.G + L.g_lane) * kVpl + v) * kPerChunk;
             off[v] = o < cols ? o : -1;
         }
     }
 };
+
+// Gather / stream the lane's chunks of one row: chunk pairs as one 32-byte access.
+template <typename T, int kVpl, int kPerChunk>
+__device__ __forceinline__ void gather_chunks(const T *row, const ChunkMap<kVpl, kPerChunk> &map, uint64_t keep,
+                                              uint4 (&raw)[kVpl]) {
+    if constexpr (kVpl == 1) {
+        if (map.off[0] >= 0) raw[0] = ld_gather16(row + map.off[0], keep);
+    } else {
+#pragma unroll
+        for (int v = 0; v < kVpl; v += 2)
+            if (map.off[v] >= 0) ld_gather32(row + map.off[v], keep, raw[v], raw[v + 1]);
+    }
+}
+template <typename T, int kVpl, int kPerChunk>
+__device__ __forceinline__ void store_chunks(T *row, const ChunkMap<kVpl, kPerChunk> &map, const uint4 (&raw)[kVpl]) {
+    if constexpr (kVpl == 1) {
+        if (map.off[0] >= 0) st_stream16(row + map.off[0], raw[0]);
+    } else {
+#pragma unroll
+        for (int v = 0; v < kVpl; v += 2)
+            if (map.off[v] >= 0) st_stream32(row + map.off[v], raw[v], raw[v + 1]);
+    }
+}
 
 template <typename T, typename I>
 struct ReduceParams {
@@ -48,7 +73,7 @@ struct MinMaxOp {
     static constexpr int kWords = kVals * (1 + kIdxWords);
     static constexpr int kUnroll = TGNN_REDUCE_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = TGNN_REDUCE_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMinBlocks = reduce_min_blocks(kWords + kUnroll * kVpl * 4);
     static constexpr int kLightMaxThreads = 256;
 
     struct Row {};
@@ -80,10 +105,7 @@ struct MinMaxOp {
         }
     }
     __device__ __forceinline__ void load(I src, Frag &f) {
-        const T *row = p.x + static_cast<int64_t>(src) * p.ldx;
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v)
-            if (map.off[v] >= 0) f.raw[v] = ld_gather16(row + map.off[v], keep);
+        gather_chunks<T, kVpl, kPer>(p.x + static_cast<int64_t>(src) * p.ldx, map, keep, f.raw);
     }
     template <bool kAll>
     __device__ __forceinline__ void consume(const Row &, State &s, const Frag (&f)[kUnroll], const I (&src)[kUnroll],
@@ -148,13 +170,18 @@ struct MinMaxOp {
     __device__ __forceinline__ void row_end(I row, const Row &, State &s, I) {
         if (L.grp != 0) return;
         T *orow = p.out + static_cast<int64_t>(row) * p.ldo;
+        uint4 packed[kVpl];
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
             float x[kPer];
 #pragma unroll
             for (int e = 0; e < kPer; ++e) x[e] = s.idx[v * kPer + e] >= 0 ? s.val[v * kPer + e] : 0.0f;
-            st_stream16(orow + map.off[v], Elem<T>::pack(x));
+            packed[v] = Elem<T>::pack(x);
+        }
+        store_chunks<T, kVpl, kPer>(orow, map, packed);
+#pragma unroll
+        for (int v = 0; v < kVpl; ++v) {
+            if (map.off[v] < 0) continue;
             if (p.arg != nullptr) {
                 I *arow = p.arg + static_cast<int64_t>(row) * p.cols + map.off[v];
                 constexpr int kPerStore = 16 / sizeof(I);
@@ -186,22 +213,25 @@ struct MinMaxOp {
 // ---- weighted sum -----------------------------------------------------------------
 // acc = sum_e w_e * x[src_e], w_e = col_scale[src] * edge_weight[e] (each
 // optional); row result = acc * row_scale[row], or acc / max(degree, 1).
+// The accumulators are float2 pairs folded with the packed fp32 add / fma of sm_100 (one
+// instruction per two features, each half rounded like the scalar instruction).
 template <typename T, typename I, int kVpl, bool kWeighted>
 struct WeightedSumOp {
     using index_t = I;
     using Params = ReduceParams<T, I>;
     static constexpr int kPer = Elem<T>::kPerChunk;
     static constexpr int kVals = kVpl * kPer;
+    static constexpr int kPairs = kVals / 2;
     static constexpr int kWords = kVals;
     static constexpr int kUnroll = TGNN_REDUCE_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = TGNN_REDUCE_MIN_BLOCKS(kVpl);
+    static constexpr int kLightMinBlocks = reduce_min_blocks(kWords + kUnroll * (kVpl * 4 + 1));
     static constexpr int kLightMaxThreads = 256;
 
     struct Row {};
     struct Carry {};
     struct State {
-        float acc[kVals];
+        float2 acc[kPairs];
     };
     struct Frag {
         uint4 raw[kVpl];
@@ -219,13 +249,10 @@ struct WeightedSumOp {
     __device__ __forceinline__ void row_begin(I, Row &) {}
     __device__ __forceinline__ void init(State &s) {
 #pragma unroll
-        for (int i = 0; i < kVals; ++i) s.acc[i] = 0.0f;
+        for (int i = 0; i < kPairs; ++i) s.acc[i] = make_float2(0.0f, 0.0f);
     }
     __device__ __forceinline__ void load(I src, Frag &f) {
-        const T *row = p.x + static_cast<int64_t>(src) * p.ldx;
-#pragma unroll
-        for (int v = 0; v < kVpl; ++v)
-            if (map.off[v] >= 0) f.raw[v] = ld_gather16(row + map.off[v], keep);
+        gather_chunks<T, kVpl, kPer>(p.x + static_cast<int64_t>(src) * p.ldx, map, keep, f.raw);
         if (kWeighted) f.w = p.col_scale != nullptr ? __ldg(p.col_scale + src) : 1.0f;
     }
     template <bool kAll>
@@ -239,51 +266,56 @@ struct WeightedSumOp {
                 w = f[u].w;
                 if (p.edge_weight != nullptr) w *= __ldg(p.edge_weight + eid[u]);
             }
+            const float2 w2 = make_float2(w, w);
 #pragma unroll
             for (int v = 0; v < kVpl; ++v) {
                 if (map.off[v] < 0) continue;
                 float x[kPer];
                 Elem<T>::unpack(f[u].raw[v], x);
 #pragma unroll
-                for (int e = 0; e < kPer; ++e) {
-                    if (kWeighted)
-                        s.acc[v * kPer + e] = fmaf(w, x[e], s.acc[v * kPer + e]);
-                    else
-                        s.acc[v * kPer + e] += x[e];
+                for (int e = 0; e < kPer; e += 2) {
+                    float2 &a = s.acc[(v * kPer + e) / 2];
+                    const float2 x2 = make_float2(x[e], x[e + 1]);
+                    a = kWeighted ? __ffma2_rn(w2, x2, a) : __fadd2_rn(a, x2);
                 }
             }
         }
     }
     __device__ __forceinline__ void merge(State &s, const State &o) {
 #pragma unroll
-        for (int i = 0; i < kVals; ++i) s.acc[i] += o.acc[i];
+        for (int i = 0; i < kPairs; ++i) s.acc[i] = __fadd2_rn(s.acc[i], o.acc[i]);
     }
     __device__ __forceinline__ void to_words(const State &s, uint32_t *w) {
 #pragma unroll
-        for (int i = 0; i < kVals; ++i) w[i] = __float_as_uint(s.acc[i]);
+        for (int i = 0; i < kPairs; ++i) {
+            w[2 * i] = __float_as_uint(s.acc[i].x);
+            w[2 * i + 1] = __float_as_uint(s.acc[i].y);
+        }
     }
     __device__ __forceinline__ void from_words(State &s, const uint32_t *w) {
 #pragma unroll
-        for (int i = 0; i < kVals; ++i) s.acc[i] = __uint_as_float(w[i]);
+        for (int i = 0; i < kPairs; ++i) s.acc[i] = make_float2(__uint_as_float(w[2 * i]), __uint_as_float(w[2 * i + 1]));
     }
     __device__ __forceinline__ void row_end(I row, const Row &, State &s, I degree) {
         if (L.grp != 0) return;
         T *orow = p.out + static_cast<int64_t>(row) * p.ldo;
         const float rs = p.row_scale != nullptr ? __ldg(p.row_scale + row) : 1.0f;
         const float denom = p.mean_by_degree ? static_cast<float>(degree > 1 ? degree : 1) : 1.0f;
+        uint4 packed[kVpl];
 #pragma unroll
         for (int v = 0; v < kVpl; ++v) {
-            if (map.off[v] < 0) continue;
             float x[kPer];
 #pragma unroll
             for (int e = 0; e < kPer; ++e) {
-                float a = s.acc[v * kPer + e];
+                const float2 pair = s.acc[(v * kPer + e) / 2];
+                float a = (e & 1) ? pair.y : pair.x;
                 if (p.mean_by_degree) a = a / denom;
                 if (kWeighted) a *= rs;
                 x[e] = a;
             }
-            st_stream16(orow + map.off[v], Elem<T>::pack(x));
+            packed[v] = Elem<T>::pack(x);
         }
+        store_chunks<T, kVpl, kPer>(orow, map, packed);
     }
     __device__ __forceinline__ void flush_row(State &) {}
     __device__ __forceinline__ void carry_init(Carry &) {}
