@@ -1,8 +1,8 @@
 """Regenerates tests/golden/*.pt from the reference project itself.
 
-Run in a container that has the reference tree (default /root/reference):
+Run where a checkout of the reference project is available:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It imports the reference's OWN code -- ``turbo_gnn/graph.py`` (CSR construction, quantile
 bucketing, repartition) and the pure-PyTorch scatter classes of
@@ -140,4 +140,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference")
+    main(sys.argv[1])

@@ -214,13 +214,13 @@ def test_tpe_exhausts_small_spaces_and_then_stops():
         got.append((cfg["p"], cfg["q"]))
         tpe.tell(cfg, float(cfg["p"]))
     assert sorted(got) == [(p, q) for p in (1, 2) for q in "abc"]
-    assert type(make_search("tpe", {"p": [1, 2]}, max_trials=8)).__name__ == "GridSearch"  # budget covers the grid
+    assert type(make_search("tpe", {"p": [1, 2]}, max_trials=8)).__name__ == "GridSearch"  # max_trials covers the grid
     assert type(make_search("tpe", _SPACE, max_trials=50)).__name__ == "TPESearch"
     with pytest.raises(ValueError):
         make_search("anneal", _SPACE, max_trials=5)
 
 
-def test_autotune_with_tpe_budget_and_trial_records(tmp_path):
+def test_autotune_with_tpe_trial_limit_and_trial_records(tmp_path):
     graph = make_graph(random_edges(60, 500, 3), 60, device="cpu")
     kern = Doubler()
     x = torch.ones(60, 8)

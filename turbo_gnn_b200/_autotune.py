@@ -245,8 +245,8 @@ class TunableKernel(ABC):
         graphs: dict[tuple, Any] = {}
         self._is_autotuning = True
         try:
-            budget = config.max_trials if config.max_trials is not None else search.size
-            for _ in range(budget):
+            limit = config.max_trials if config.max_trials is not None else search.size
+            for _ in range(limit):
                 cfg = search.ask()
                 if cfg is None:
                     break

@@ -114,7 +114,7 @@ class TPESearch(GridSearch):
 
 
 def make_search(kind: str, space: dict[str, list], max_trials: int | None = None, seed: int = 0):
-    """``"grid"`` or ``"tpe"``; a TPE request falls back to the grid when the budget covers it."""
+    """``"grid"`` or ``"tpe"``; a TPE request falls back to the grid when ``max_trials`` covers every combination."""
     grid = GridSearch(space)
     if kind == "grid" or max_trials is None or grid.size <= max_trials:
         return grid
