@@ -191,13 +191,14 @@ bool wide_rows_ok(const tgnn_mat &m) {
 #define TGNN_ATTN_MAX_VPL 8
 #endif
 
-Geometry make_attn_geometry(int64_t cols, int head_dim, int32_t dtype) {
+Geometry make_attn_geometry(int64_t cols, int head_dim, int32_t dtype, int max_vpl) {
+    if (max_vpl <= 0) max_vpl = TGNN_ATTN_MAX_VPL;
     const int per = dtype == TGNN_F32 ? 4 : 8;
     const int64_t chunks = (cols + per - 1) / per;
     const int chunks_per_head = head_dim / per > 0 ? head_dim / per : 1;
     Geometry g;
     g.vpl = 1;
-    while (g.vpl < TGNN_ATTN_MAX_VPL && g.vpl * 2 <= chunks_per_head && 32 * g.vpl < chunks) g.vpl *= 2;
+    while (g.vpl < max_vpl && g.vpl * 2 <= chunks_per_head && 32 * g.vpl < chunks) g.vpl *= 2;
     const int64_t lanes = (chunks + g.vpl - 1) / g.vpl;
     int lanes_per_head = chunks_per_head / g.vpl;
     if (lanes_per_head < 1) lanes_per_head = 1;

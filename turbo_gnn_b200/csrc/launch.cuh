@@ -89,8 +89,9 @@ Geometry make_geometry(int64_t cols, int chunk_elems, int min_group_lanes, bool 
 // Base address and row pitch multiples of 32 bytes, column count a multiple of two chunks.
 bool wide_rows_ok(const tgnn_mat &m);
 // Geometry of the attention ops: every lane owns `vpl` consecutive chunks that lie
-// inside one head (vpl <= head_dim / chunk_elems); a lane group holds whole heads.
-Geometry make_attn_geometry(int64_t cols, int head_dim, int32_t dtype);
+// inside one head (vpl <= head_dim / chunk_elems, and <= max_vpl; 0 = the build's default); a
+// lane group holds whole heads and rows wider than a warp's lanes go to feature slices.
+Geometry make_attn_geometry(int64_t cols, int head_dim, int32_t dtype, int max_vpl = 0);
 // check_mat plus 32-byte alignment of base and pitch: the attention ops use 256-bit accesses.
 int32_t check_attn_mat(const tgnn_mat &m, const char *name, int64_t rows, int64_t cols, int32_t dtype);
 

@@ -85,6 +85,62 @@ struct HeadMap {
     }
 };
 
+// Packed fp32 arithmetic (sm_100: one instruction for two lanes of a float2, each half rounded
+// like the scalar instruction).  TGNN_PACKED_F32=0 builds the scalar forms.
+#ifndef TGNN_PACKED_F32
+#define TGNN_PACKED_F32 1
+#endif
+
+// sum_i a[i] * b[i]; the packed form keeps an even and an odd partial sum.
+template <int kN>
+__device__ __forceinline__ float dot_span(const float (&a)[kN], const float (&b)[kN]) {
+#if TGNN_PACKED_F32
+    float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < kN; i += 2) acc = __ffma2_rn(make_float2(a[i], a[i + 1]), make_float2(b[i], b[i + 1]), acc);
+    return acc.x + acc.y;
+#else
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kN; ++i) acc = fmaf(a[i], b[i], acc);
+    return acc;
+#endif
+}
+
+// y[i] += s * x[i]
+template <int kN>
+__device__ __forceinline__ void axpy_span(float s, const float (&x)[kN], float *y) {
+#if TGNN_PACKED_F32
+    const float2 s2 = make_float2(s, s);
+#pragma unroll
+    for (int i = 0; i < kN; i += 2) {
+        const float2 r = __ffma2_rn(s2, make_float2(x[i], x[i + 1]), make_float2(y[i], y[i + 1]));
+        y[i] = r.x;
+        y[i + 1] = r.y;
+    }
+#else
+#pragma unroll
+    for (int i = 0; i < kN; ++i) y[i] = fmaf(s, x[i], y[i]);
+#endif
+}
+
+// y[i] *= s
+template <int kN>
+__device__ __forceinline__ void scale_span(float s, float *y) {
+#if TGNN_PACKED_F32
+    const float2 s2 = make_float2(s, s);
+#pragma unroll
+    for (int i = 0; i < kN; i += 2) {
+        const float2 r = __fmul2_rn(s2, make_float2(y[i], y[i + 1]));
+        y[i] = r.x;
+        y[i + 1] = r.y;
+    }
+#else
+#pragma unroll
+    for (int i = 0; i < kN; ++i) y[i] *= s;
+#endif
+}
+
 // Running softmax-weighted sum of gathered rows (base-2 domain).
 template <int kVals>
 struct SoftmaxAcc {
@@ -110,8 +166,7 @@ struct SoftmaxAcc {
             // 0 when m was -inf; a lane group that still has no edge (m_new = -inf) is left alone
             const float corr = m_new == -INFINITY ? 1.0f : fast_exp2(m - m_new);
             s *= corr;
-#pragma unroll
-            for (int i = 0; i < kVals; ++i) acc[i] *= corr;
+            scale_span<kVals>(corr, acc);
             m = m_new;
         }
         if (!kAll && m == -INFINITY) return;  // this lane group has seen no edge yet
@@ -119,8 +174,7 @@ struct SoftmaxAcc {
         for (int j = 0; j < kU; ++j) {
             const float p = fast_exp2(sc[j] - m);
             s += p;
-#pragma unroll
-            for (int i = 0; i < kVals; ++i) acc[i] = fmaf(p, x[j][i], acc[i]);
+            axpy_span<kVals>(p, x[j], acc);
         }
     }
     __device__ __forceinline__ void merge(const SoftmaxAcc &o) {

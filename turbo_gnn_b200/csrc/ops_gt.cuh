@@ -102,10 +102,7 @@ struct GtFwdOp : GtBase<T, I, kVpl> {
                 f[u].v.clear();
             }
             f[u].q.template to_f32<T>(x[u]);
-            float acc = 0.0f;
-#pragma unroll
-            for (int i = 0; i < kVals; ++i) acc = fmaf(x[u][i], rc.k[i], acc);
-            sc[u] = acc;
+            sc[u] = dot_span<kVals>(x[u], rc.k);
             f[u].v.template to_f32<T>(x[u]);
         }
         hm.finish(sc);
@@ -190,14 +187,8 @@ struct GtBwdDstOp : GtBase<T, I, kVpl> {
             float xv[kVals];
             f[u].q.template to_f32<T>(xq[u]);
             f[u].v.template to_f32<T>(xv);
-            float ps = 0.0f, pd = 0.0f;
-#pragma unroll
-            for (int i = 0; i < kVals; ++i) {
-                ps = fmaf(xq[u][i], rc.k[i], ps);
-                pd = fmaf(xv[i], rc.dO[i], pd);
-            }
-            d[u] = ps;
-            d[kUnroll + u] = pd;
+            d[u] = dot_span<kVals>(xq[u], rc.k);
+            d[kUnroll + u] = dot_span<kVals>(xv, rc.dO);
         }
         hm.finish(d);
 #pragma unroll
@@ -205,8 +196,7 @@ struct GtBwdDstOp : GtBase<T, I, kVpl> {
             float alpha = fast_exp2(d[u] - rc.lse2);
             if (!kAll && !ok[u]) alpha = 0.0f;
             const float ds = alpha * (d[kUnroll + u] - rc.delta) * p.scale;
-#pragma unroll
-            for (int i = 0; i < kVals; ++i) s.a[i] = fmaf(ds, xq[u][i], s.a[i]);
+            axpy_span<kVals>(ds, xq[u], s.a);
         }
     }
     __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
@@ -278,14 +268,8 @@ struct GtBwdSrcOp : GtBase<T, I, kVpl> {
             }
             f[u].k.template to_f32<T>(xk[u]);
             f[u].d.template to_f32<T>(xd[u]);
-            float ps = 0.0f, pd = 0.0f;
-#pragma unroll
-            for (int i = 0; i < kVals; ++i) {
-                ps = fmaf(xk[u][i], rc.q[i], ps);
-                pd = fmaf(xd[u][i], rc.v[i], pd);
-            }
-            d[u] = ps;
-            d[kUnroll + u] = pd;
+            d[u] = dot_span<kVals>(xk[u], rc.q);
+            d[kUnroll + u] = dot_span<kVals>(xd[u], rc.v);
         }
         hm.finish(d);
 #pragma unroll
@@ -293,11 +277,8 @@ struct GtBwdSrcOp : GtBase<T, I, kVpl> {
             float alpha = fast_exp2(fmaf(-f[u].lse, kLog2e, d[u]));
             if (!kAll && !ok[u]) alpha = 0.0f;
             const float ds = alpha * (d[kUnroll + u] - f[u].delta) * p.scale;
-#pragma unroll
-            for (int i = 0; i < kVals; ++i) {
-                s.a[i] = fmaf(ds, xk[u][i], s.a[i]);
-                s.a[kVals + i] = fmaf(alpha, xd[u][i], s.a[kVals + i]);
-            }
+            axpy_span<kVals>(ds, xk[u], s.a);
+            axpy_span<kVals>(alpha, xd[u], s.a + kVals);
         }
     }
     __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
