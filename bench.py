@@ -248,7 +248,10 @@ class Job:
             return {
                 "tgnn_gt_forward": E * (2 * Fs + i) + R * (2 * Fs + 4 * H),
                 "tgnn_gt_backward_dst": E * (2 * Fs + i) + R * (3 * Fs + 8 * H),
-                "tgnn_gt_backward_src": E * (2 * Fs + i + 8 * H) + R * (4 * Fs),
+                # + 4H per edge when it also hands dS to the dK pass (single GPU)
+                "tgnn_gt_backward_src": E * (2 * Fs + i + 8 * H + (0 if self.shard else 4 * H)) + R * (4 * Fs),
+                # dK from handed-over dS: one gathered row, the column id, the edge position and dS
+                "tgnn_gt_backward_dk": E * (Fs + 2 * i + 4 * H) + R * Fs,
                 "tgnn_head_dot": R * (2 * Fs + 4 * H),
             }
         if self.op == "gatv2":

@@ -38,7 +38,7 @@
 extern "C" {
 #endif
 
-#define TGNN_ABI_VERSION 2
+#define TGNN_ABI_VERSION 3
 
 typedef enum tgnn_status {
     TGNN_OK = 0,
@@ -150,7 +150,8 @@ typedef enum tgnn_op {
     TGNN_OP_GATV2_BWD_SRC = 4,
     TGNN_OP_GT_FWD = 5,
     TGNN_OP_GT_BWD_DST = 6,
-    TGNN_OP_GT_BWD_SRC = 7
+    TGNN_OP_GT_BWD_SRC = 7,
+    TGNN_OP_GT_BWD_DK = 8
 } tgnn_op;
 
 /* Bytes of caller scratch `op` needs for a schedule with `num_chunks` hub
@@ -433,8 +434,30 @@ typedef struct tgnn_gt_bwd_src_args {
     tgnn_mat dv; /* [rows of csr_t, H*D] */
     void *workspace;
     size_t workspace_bytes;
+    float *ds_out; /* optional [edges of csr_t, H]: scale * dS of every edge and head, for
+                      tgnn_gt_backward_dk; NULL = not wanted */
 } tgnn_gt_bwd_src_args;
 int32_t tgnn_gt_backward_src(const tgnn_gt_bwd_src_args *a);
+
+/* Destination-side half from handed-over dS (no counterpart in the reference, which recomputes
+ * dS in both halves, csrc/gt/gt_backward.cu:62-245): dk[i] = sum_j ds[pos(i,j)] q[j] over the
+ * forward CSR, where ds is what tgnn_gt_backward_src stored and edge_pos[e] is the position of
+ * forward-CSR edge e in the transposed CSR.  One gathered row per edge instead of the two of
+ * tgnn_gt_backward_dst; run it after the source-side half. */
+typedef struct tgnn_gt_bwd_dk_args {
+    tgnn_exec exec;
+    tgnn_csr csr;
+    tgnn_schedule sched;
+    tgnn_mat q;           /* [cols, H*D] */
+    const float *ds;      /* [edges, H], order of the transposed CSR */
+    const void *edge_pos; /* [edges], index type of the CSR */
+    int32_t heads;
+    int32_t head_dim;
+    tgnn_mat dk; /* [rows, H*D] */
+    void *workspace;
+    size_t workspace_bytes;
+} tgnn_gt_bwd_dk_args;
+int32_t tgnn_gt_backward_dk(const tgnn_gt_bwd_dk_args *a);
 
 /* ---- graph construction ---------------------------------------------------- */
 

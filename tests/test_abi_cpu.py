@@ -30,6 +30,7 @@ STRUCTS = {
     "tgnn_gt_fwd_args": _abi.GtFwdArgs,
     "tgnn_gt_bwd_dst_args": _abi.GtBwdDstArgs,
     "tgnn_gt_bwd_src_args": _abi.GtBwdSrcArgs,
+    "tgnn_gt_bwd_dk_args": _abi.GtBwdDkArgs,
     "tgnn_coo_to_csr_args": _abi.CooToCsrArgs,
     "tgnn_degree_order_stats_args": _abi.DegreeOrderStatsArgs,
     "tgnn_partition_rows_args": _abi.PartitionRowsArgs,

@@ -60,3 +60,38 @@ def test_tile_table_device_matches_definition():
         cols = idx[ptr[r]: ptr[r + 1]]
         for t in range(tiles + 1):
             assert int(table[t, r]) == int(ptr[r]) + int((cols < t * span).sum())
+
+
+# ---- graph-transformer backward with dS handed from the source-side half to the dK pass ------------
+
+
+@pytest.mark.parametrize("symmetric", [False, True])
+@pytest.mark.parametrize("tiles", [1, 3])
+def test_gt_backward_hand_over_matches_both_the_oracle_and_the_recomputing_halves(symmetric, tiles):
+    ei, g = _graph(torch.int32, 0.9, seed=41, symmetric=symmetric)
+    assert _C.edge_positions(g.forward_indptr, g.forward_indices, g.backward_indptr, g.backward_indices) is not None
+    results = {}
+    for mode in (None, False):
+        with _C.hub_tier(column_tiles=tiles, gt_hand_over=mode):
+            results[mode] = _gt_case(ei, g, 4, 32, torch.float32)
+        assert max(results[mode].values()) <= TOL[torch.float32], (mode, results[mode])
+
+
+def test_edge_positions_are_the_transpose_permutation():
+    ei, g = _graph(torch.int64, 0.9, seed=42)
+    pos = _C.edge_positions(g.forward_indptr, g.forward_indices, g.backward_indptr, g.backward_indices).long()
+    fp, fi = g.forward_indptr.long(), g.forward_indices.long()
+    bp, bi = g.backward_indptr.long(), g.backward_indices.long()
+    dst = torch.repeat_interleave(torch.arange(fp.numel() - 1, device=fp.device), fp[1:] - fp[:-1])
+    src_t = torch.repeat_interleave(torch.arange(bp.numel() - 1, device=bp.device), bp[1:] - bp[:-1])
+    assert torch.equal(bi[pos], dst) and torch.equal(src_t[pos], fi)  # same edge in both orderings
+    assert torch.equal(torch.sort(pos).values, torch.arange(pos.numel(), device=pos.device))
+
+
+def test_hand_over_falls_back_when_the_second_csr_is_not_the_sorted_transpose():
+    ei, g = _graph(torch.int32, 0.9, seed=43)
+    flipped = g.backward_indices.clone()
+    bp = g.backward_indptr.long()
+    r = int(torch.argmax(bp[1:] - bp[:-1]))  # reverse the columns of the longest row
+    flipped[bp[r]: bp[r + 1]] = flipped[bp[r]: bp[r + 1]].flip(0)
+    assert _C.edge_positions(g.forward_indptr, g.forward_indices, g.backward_indptr, flipped) is None

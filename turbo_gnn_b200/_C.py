@@ -41,12 +41,13 @@ _hub_cfg = {
     "cta_min_degree": _schedule.DEFAULT_CTA_MIN_DEGREE,
     "sort_by_degree": True,
     "column_tiles": None,  # attention ops: None = automatic, 1 = off, k = k column tiles
+    "gt_hand_over": None,  # graph-transformer backward: False = both halves recompute dS
 }
 
 
 def configure_hub_tier(**values) -> dict:
     """Set tier parameters (``chunk_edges``, ``hub_min_degree``, ``cta_min_degree``, ``sort_by_degree``,
-    ``column_tiles``)
+    ``column_tiles``, ``gt_hand_over``)
     for later calls; a value of ``None`` selects the automatic threshold.  Returns the previous values."""
     unknown = set(values) - set(_hub_cfg)
     if unknown:
@@ -291,6 +292,7 @@ def clear_graph_cache():
     """Forget cached transposes, schedules and norm scales (``csrc/turbo_gnn.cpp:73``)."""
     _spmm_graphs.clear()
     _schedule.clear_schedule_cache()
+    _edge_pos_cache.clear()
 
 
 def _bucket(indptr):
@@ -749,10 +751,12 @@ def gt_backward_dst(row_ptr, col_idx, Q, K, V, dO, lse, delta, scale, light_node
 
 
 def gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_nodes, heavy_nodes, light_warps=1,
-                    heavy_warps=8):
+                    heavy_warps=8, ds_out=None):
     """Source-side pass over the transposed CSR: ``(dQ, dV)``.
 
     Q, V: one row per row of the transposed CSR; K, dO, lse, delta: one row per column of it.
+    ``ds_out`` (fp32 ``[E, H]``, optional) receives ``scale * dS`` of every edge and head in the
+    order of the transposed CSR, for :func:`gt_backward_dk`.
     """
     n_src, heads, d = Q.shape
     dp = _padded_head_dim(d)
@@ -781,9 +785,91 @@ def gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_
             dv=_abi.mat_of(dv),
             workspace=_abi.ptr(ws),
             workspace_bytes=ws_bytes,
+            ds_out=_abi.ptr(ds_out),
         )
         _abi.call("tgnn_gt_backward_src", args)
     return _strip(dq, d), _strip(dv, d)
+
+
+def gt_backward_dk(row_ptr, col_idx, Q, ds, edge_pos, n_rows, light_nodes, heavy_nodes, light_warps=1,
+                   heavy_warps=8):
+    """Destination-side pass from handed-over dS: ``dK[i] = sum_j ds[edge_pos[e_ij]] * Q[j]`` over the
+    forward CSR (``ds`` from :func:`gt_backward_src`, ``edge_pos`` from :func:`edge_positions`)."""
+    n_src, heads, d = Q.shape
+    dp = _padded_head_dim(d)
+    q_in = _head_rows(Q, dp)
+    dk = torch.empty((n_rows, heads, dp), dtype=Q.dtype, device=Q.device)
+    if n_rows > 0:
+        sched = _attn_sched(row_ptr, col_idx, light_nodes, heavy_nodes, n_src, heads * dp * q_in.element_size())
+        ws, ws_bytes = _scratch(_abi.OP_GT_BWD_DK, sched, q_in, row_ptr.dtype, heads * dp, n_rows)
+        args = _abi.GtBwdDkArgs(
+            exec=_abi.exec_of(q_in),
+            csr=_abi.csr_of(row_ptr, col_idx, n_src),
+            sched=sched.to_struct(_LIGHT_CTA_WARPS, _clamp_heavy(heavy_warps), _clamp_light(light_warps)),
+            q=_abi.mat_of(q_in),
+            ds=_abi.ptr(ds),
+            edge_pos=_abi.ptr(edge_pos),
+            heads=heads,
+            head_dim=dp,
+            dk=_abi.mat_of(dk),
+            workspace=_abi.ptr(ws),
+            workspace_bytes=ws_bytes,
+        )
+        _abi.call("tgnn_gt_backward_dk", args)
+    return _strip(dk, d)
+
+
+class _EdgePositionCache:
+    """``edge_positions`` results keyed on the identity of the four CSR arrays."""
+
+    def __init__(self, slots: int = 16):
+        self._slots, self._items = slots, OrderedDict()
+
+    def get(self, arrays):
+        key = tuple(id(a) for a in arrays)
+        hit = self._items.get(key)
+        if hit is not None and all(r() is a for r, a in zip(hit[0], arrays)):
+            self._items.move_to_end(key)
+            return True, hit[1]
+        return False, None
+
+    def put(self, arrays, value):
+        self._items[tuple(id(a) for a in arrays)] = (tuple(weakref.ref(a) for a in arrays), value)
+        while len(self._items) > self._slots:
+            self._items.popitem(last=False)
+
+    def clear(self):
+        self._items.clear()
+
+
+_edge_pos_cache = _EdgePositionCache()
+
+
+def edge_positions(row_ptr, col_idx, row_ptr_T, col_idx_T):
+    """For every edge of the forward CSR its position in the transposed CSR (index dtype), or
+    ``None`` when the second CSR is not the (row, column)-sorted transpose of the first.  Built
+    once per graph with the library's sort and cached."""
+    arrays = (row_ptr, col_idx, row_ptr_T, col_idx_T)
+    hit, value = _edge_pos_cache.get(arrays)
+    if hit:
+        return value
+    from . import graph_build
+
+    ptr = _schedule._signed(row_ptr)
+    n_rows, n_src, num_edges = ptr.numel() - 1, row_ptr_T.numel() - 1, col_idx.numel()
+    value = None
+    if 0 < num_edges < (1 << 31) and col_idx_T.numel() == num_edges:
+        dst_of_edge = torch.repeat_interleave(torch.arange(n_rows, device=ptr.device, dtype=ptr.dtype),
+                                              (ptr[1:] - ptr[:-1]).long(), output_size=num_edges)
+        t_ptr, t_idx, order = graph_build.coo_to_csr(_schedule._signed(col_idx), dst_of_edge, max(n_rows, n_src),
+                                                     ptr.dtype, want_order=True)
+        same = torch.equal(t_ptr[: n_src + 1], _schedule._signed(row_ptr_T)) and torch.equal(
+            t_idx, _schedule._signed(col_idx_T))
+        if same:
+            value = torch.empty(num_edges, dtype=ptr.dtype, device=ptr.device)
+            value[order.long()] = torch.arange(num_edges, device=ptr.device, dtype=ptr.dtype)
+    _edge_pos_cache.put(arrays, value)
+    return value
 
 
 def gt_backward_csr_mh(row_ptr, col_idx, row_ptr_T, col_idx_T, Q, K, V, O, dO, logsumexp, scale, light_nodes,
@@ -805,8 +891,22 @@ def gt_backward_csr_mh(row_ptr, col_idx, row_ptr_T, col_idx_T, Q, K, V, O, dO, l
     delta = head_dot(_head_rows(dO, dp), _head_rows(O.reshape(n_rows, heads, d), dp))
     lse = logsumexp.contiguous()
     lw, hw = light_warps_per_block, heavy_warps_per_block
-    dk = gt_backward_dst(row_ptr, col_idx, Q, K, V, dO, lse, delta, scale, fwd_light_nodes, fwd_heavy_nodes, lw, hw)
-    dq, dv = gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_nodes, heavy_nodes, lw, hw)
+    # Hand-over: the source-side half stores dS per edge and dK becomes a weighted sum that gathers
+    # one row per edge instead of two.  Needs the edge permutation between the two CSRs and row
+    # lists that cover every source row (the stored dS of an unlisted row would be missing).
+    pos = None
+    if _hub_cfg["gt_hand_over"] is not False and light_nodes.numel() + heavy_nodes.numel() == row_ptr_T.numel() - 1:
+        pos = edge_positions(row_ptr, col_idx, row_ptr_T, col_idx_T)
+    if pos is None:
+        dk = gt_backward_dst(row_ptr, col_idx, Q, K, V, dO, lse, delta, scale, fwd_light_nodes, fwd_heavy_nodes, lw,
+                             hw)
+        dq, dv = gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_nodes, heavy_nodes, lw,
+                                 hw)
+        return dq, dk, dv
+    ds = torch.empty((col_idx_T.numel(), heads), dtype=torch.float32, device=Q.device)
+    dq, dv = gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_nodes, heavy_nodes, lw, hw,
+                             ds_out=ds)
+    dk = gt_backward_dk(row_ptr, col_idx, Q, ds, pos, n_rows, fwd_light_nodes, fwd_heavy_nodes, lw, hw)
     return dq, dk, dv
 
 

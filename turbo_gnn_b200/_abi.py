@@ -19,7 +19,7 @@ from pathlib import Path
 import torch
 
 LIB_NAME = "libturbo_gnn_b200.so"
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 OK = 0
 F32, F16, BF16 = 0, 1, 2
@@ -28,7 +28,7 @@ REDUCE = {"min": 0, "max": 1, "sum": 2, "mean": 3}
 NORM = {"none": 0, "right": 1, "left": 2, "both": 3}
 OP_REDUCE_MINMAX, OP_WEIGHTED_SUM = 0, 1
 OP_GATV2_FWD, OP_GATV2_BWD_DST, OP_GATV2_BWD_SRC = 2, 3, 4
-OP_GT_FWD, OP_GT_BWD_DST, OP_GT_BWD_SRC = 5, 6, 7
+OP_GT_FWD, OP_GT_BWD_DST, OP_GT_BWD_SRC, OP_GT_BWD_DK = 5, 6, 7, 8
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 _ITYPES = {torch.int32: I32, torch.int64: I64, torch.uint32: I32, torch.uint64: I64}
@@ -267,6 +267,23 @@ class GtBwdSrcArgs(C.Structure):
         ("dv", Mat),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
+        ("ds_out", C.c_void_p),
+    ]
+
+
+class GtBwdDkArgs(C.Structure):
+    _fields_ = [
+        ("exec", Exec),
+        ("csr", Csr),
+        ("sched", Schedule),
+        ("q", Mat),
+        ("ds", C.c_void_p),
+        ("edge_pos", C.c_void_p),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("dk", Mat),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -335,6 +352,7 @@ ENTRY_POINTS = {
     "tgnn_gt_forward": GtFwdArgs,
     "tgnn_gt_backward_dst": GtBwdDstArgs,
     "tgnn_gt_backward_src": GtBwdSrcArgs,
+    "tgnn_gt_backward_dk": GtBwdDkArgs,
     "tgnn_graph_workspace_bytes": None,
     "tgnn_coo_to_csr": CooToCsrArgs,
     "tgnn_degree_order_stats": DegreeOrderStatsArgs,

@@ -231,7 +231,8 @@ static size_t state_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t slot
         case TGNN_OP_GATV2_BWD_SRC: return tgnn::gatv2_scratch_bytes(op, dtype, itype, slots, feat_cols);
         case TGNN_OP_GT_FWD:
         case TGNN_OP_GT_BWD_DST:
-        case TGNN_OP_GT_BWD_SRC: return tgnn::gt_scratch_bytes(op, dtype, itype, slots, feat_cols);
+        case TGNN_OP_GT_BWD_SRC:
+        case TGNN_OP_GT_BWD_DK: return tgnn::gt_scratch_bytes(op, dtype, itype, slots, feat_cols);
         default: return 0;
     }
 }

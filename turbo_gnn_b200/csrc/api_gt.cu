@@ -56,6 +56,7 @@ size_t gt_scratch_bytes(int32_t op, int32_t dtype, int32_t itype, int64_t num_ch
         if (op == TGNN_OP_GT_FWD) words = words_of<GtFwdOp>(dtype, itype, vpl);
         if (op == TGNN_OP_GT_BWD_DST) words = words_of<GtBwdDstOp>(dtype, itype, vpl);
         if (op == TGNN_OP_GT_BWD_SRC) words = words_of<GtBwdSrcOp>(dtype, itype, vpl);
+        if (op == TGNN_OP_GT_BWD_DK) words = words_of<GtBwdDkOp>(dtype, itype, vpl);
         const int64_t lanes = (chunks + vpl - 1) / vpl;
         const size_t slices = static_cast<size_t>((lanes + 31) / 32);
         const size_t need = static_cast<size_t>(num_chunks) * slices * words * 32 * sizeof(uint32_t);
@@ -154,7 +155,39 @@ extern "C" int32_t tgnn_gt_backward_src(const tgnn_gt_bwd_src_args *a) {
         p.ldo0 = a->dq.row_stride;
         p.out1 = static_cast<T *>(a->dv.data);
         p.ldo1 = a->dv.row_stride;
+        p.ds_out = a->ds_out;
         return run_tiers<GtBwdSrcOp<T, I, decltype(vt)::value>>(p, a->csr_t, a->sched, a->exec, geo, a->workspace,
                                                                 a->workspace_bytes, false, true);
+    });
+}
+
+extern "C" int32_t tgnn_gt_backward_dk(const tgnn_gt_bwd_dk_args *a) {
+    TGNN_REQUIRE(a != nullptr, TGNN_ERR_INVALID_ARGUMENT, "null argument block");
+    TGNN_TRY(check_exec(a->exec));
+    TGNN_TRY(check_csr(a->csr));
+    TGNN_TRY(check_schedule(a->sched, a->csr));
+    const int64_t cols = a->q.cols;
+    TGNN_TRY(check_attn_mat(a->q, "Q", a->csr.num_cols, cols, -1));
+    TGNN_TRY(check_attn_mat(a->dk, "dK", a->csr.num_rows, cols, a->q.dtype));
+    TGNN_TRY(check_gt_heads(a->heads, a->head_dim, cols));
+    TGNN_REQUIRE((a->ds != nullptr && a->edge_pos != nullptr) || a->csr.num_edges == 0, TGNN_ERR_INVALID_ARGUMENT,
+                 "ds or edge_pos is null");
+    if (a->csr.num_rows == 0) return TGNN_OK;
+    const Geometry geo = make_attn_geometry(cols, a->head_dim, a->q.dtype);
+    return dispatch_tiv(a->q.dtype, a->csr.itype, geo.vpl, [&](auto tt, auto it, auto vt) -> int32_t {
+        using T = typename decltype(tt)::type;
+        using I = typename decltype(it)::type;
+        GtParams<T> p{};
+        p.q = static_cast<const T *>(a->q.data);
+        p.ldq = a->q.row_stride;
+        p.cols = static_cast<int>(cols);
+        p.heads = a->heads;
+        p.head_dim = a->head_dim;
+        p.ds = a->ds;
+        p.edge_pos = a->edge_pos;
+        p.out0 = static_cast<T *>(a->dk.data);
+        p.ldo0 = a->dk.row_stride;
+        return run_tiers<GtBwdDkOp<T, I, decltype(vt)::value>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
+                                                               a->workspace_bytes, false, true);
     });
 }

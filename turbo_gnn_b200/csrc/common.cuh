@@ -25,6 +25,9 @@
 #ifndef TGNN_MIN_BLOCKS_GT_BWD_SRC
 #define TGNN_MIN_BLOCKS_GT_BWD_SRC(vpl) 4
 #endif
+#ifndef TGNN_MIN_BLOCKS_GT_BWD_DK
+#define TGNN_MIN_BLOCKS_GT_BWD_DK(vpl) ((vpl) >= 4 ? 4 : 6)
+#endif
 #ifndef TGNN_MIN_BLOCKS_GATV2
 #define TGNN_MIN_BLOCKS_GATV2(vpl) ((vpl) >= 4 ? 4 : 5)
 #endif

@@ -7,6 +7,12 @@
 //   dk_i = sum_j scale dS_ij q_j     dq_j = sum_i scale dS_ij k_i     dv_j = sum_i alpha_ij dO_i
 //
 // Both backward halves recompute alpha from the saved log-sum-exp; neither uses atomics.
+//
+// Hand-over variant of the backward pass: the source-side pass, which has every operand of dS_ij
+// at hand, also stores scale * dS_ij per edge and head (in the order of the transposed CSR);
+// dk_i is then a plain weighted sum of q_j over the forward CSR (GtBwdDkOp) that gathers one row
+// per edge instead of two and finds its weight through the edge permutation between the two
+// orderings.  It replaces GtBwdDstOp when the host has that permutation.
 #pragma once
 
 #include "ops_attn.cuh"
@@ -25,6 +31,9 @@ struct GtParams {
     int64_t ldd;
     const float *lse;
     const float *delta;
+    float *ds_out;        // bwd src, optional: [edges of the transposed CSR, heads] scale * dS
+    const float *ds;      // bwd dk: the same array
+    const void *edge_pos; // bwd dk: position in the transposed CSR of every forward-CSR edge
     T *out0;  // out (forward) | dk (bwd dst) | dq (bwd src)
     int64_t ldo0;
     T *out1;  // dv (bwd src)
@@ -238,7 +247,22 @@ struct GtBwdSrcOp : GtBase<T, I, kVpl> {
         float delta;
     };
 
-    __device__ __forceinline__ GtBwdSrcOp(const Params &p_, const Lanes &L_) : B(p_, L_) {}
+    // Hand-over of dS: lane t of an edge's lane group fetches the value of the group's t-th head
+    // (lane `ds_from`), so that the heads of one edge leave as one run of consecutive words.
+    int ds_from;
+    int ds_head;  // head this lane stores, -1: none, -2: no hand-over in this call
+
+    __device__ __forceinline__ GtBwdSrcOp(const Params &p_, const Lanes &L_) : B(p_, L_) {
+        ds_from = L.lane;
+        ds_head = -2;
+        if (p.ds_out != nullptr) {
+            const int heads_here = L.G / hm.lanes_per_head;
+            const int t = L.g_lane < heads_here ? L.g_lane : 0;
+            ds_from = (L.lane - L.g_lane) + t * hm.lanes_per_head;
+            const int head = (L.slice * L.G * kVals) / p.head_dim + L.g_lane;
+            ds_head = (L.g_lane < heads_here && head < p.heads) ? head : -1;
+        }
+    }
     __device__ __forceinline__ void row_begin(I row, Row &rc) {
         load_span_f32<T, kVpl>(p.q + static_cast<int64_t>(row) * p.ldq, map.off, rc.q);
         load_span_f32<T, kVpl>(p.v + static_cast<int64_t>(row) * p.ldv, map.off, rc.v);
@@ -256,7 +280,7 @@ struct GtBwdSrcOp : GtBase<T, I, kVpl> {
     }
     template <bool kAll>
     __device__ __forceinline__ void consume(const Row &rc, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
-                                            const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
+                                            const I (&eid)[kUnroll], const bool (&ok)[kUnroll]) {
         float d[2 * kUnroll];
         float xk[kUnroll][kVals], xd[kUnroll][kVals];
 #pragma unroll
@@ -277,6 +301,11 @@ struct GtBwdSrcOp : GtBase<T, I, kVpl> {
             float alpha = fast_exp2(fmaf(-f[u].lse, kLog2e, d[u]));
             if (!kAll && !ok[u]) alpha = 0.0f;
             const float ds = alpha * (d[kUnroll + u] - f[u].delta) * p.scale;
+            if (ds_head >= -1) {  // dS wanted (ds_head == -1: this lane only takes part in the shuffle)
+                const float mine = __shfl_sync(kFull, ds, ds_from);
+                if (ds_head >= 0 && (kAll || ok[u]))
+                    __stcs(p.ds_out + static_cast<int64_t>(eid[u]) * p.heads + ds_head, mine);  // streamed
+            }
             axpy_span<kVals>(ds, xk[u], s.a);
             axpy_span<kVals>(alpha, xd[u], s.a + kVals);
         }
@@ -288,6 +317,60 @@ struct GtBwdSrcOp : GtBase<T, I, kVpl> {
         if (L.grp != 0 || !map.live) return;
         store_span_f32<T, kVpl>(p.out0 + static_cast<int64_t>(row) * p.ldo0, map.off, s.a);
         store_span_f32<T, kVpl>(p.out1 + static_cast<int64_t>(row) * p.ldo1, map.off, s.a + kVals);
+    }
+    __device__ __forceinline__ void flush_row(State &) {}
+    __device__ __forceinline__ void carry_init(Carry &) {}
+    __device__ __forceinline__ void carry_add(Carry &, const State &) {}
+    __device__ __forceinline__ void carry_flush(Carry &, uint32_t *) {}
+};
+
+// ---- backward, destination side from handed-over dS: dk_i = sum_j (scale dS_ij) q_j ----------
+template <typename T, typename I, int kVpl>
+struct GtBwdDkOp : GtBase<T, I, kVpl> {
+    using B = GtBase<T, I, kVpl>;
+    using typename B::index_t;
+    using typename B::Params;
+    using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p;
+    static constexpr int kWords = kVals;
+    static constexpr int kUnroll = 2 * TGNN_ATTN_UNROLL(kVpl);
+    static constexpr int kCarryWords = 0;
+    static constexpr int kLightMinBlocks = TGNN_MIN_BLOCKS_GT_BWD_DK(kVpl);
+    static constexpr int kLightMaxThreads = TGNN_ATTN_LIGHT_THREADS;
+    static constexpr bool kEdgeStream = true;
+
+    struct Row {};
+    using State = SumAcc<kVals>;
+    using Carry = NoCarry;
+    struct Frag {
+        Span<kVpl> q;
+        float w;
+    };
+
+    __device__ __forceinline__ GtBwdDkOp(const Params &p_, const Lanes &L_) : B(p_, L_) {}
+    __device__ __forceinline__ const I *edge_stream() const { return static_cast<const I *>(p.edge_pos); }
+    __device__ __forceinline__ void row_begin(I, Row &) {}
+    __device__ __forceinline__ void init(State &s) { s.init(); }
+    __device__ __forceinline__ void load_edge(I src, I pos, Frag &f) {
+        gather_span<T, kVpl>(p.q + static_cast<int64_t>(src) * p.ldq, map.off, keep, f.q);
+        f.w = __ldcs(p.ds + static_cast<int64_t>(pos) * p.heads + hm.head);  // read once
+    }
+    template <bool kAll>
+    __device__ __forceinline__ void consume(const Row &, State &s, Frag (&f)[kUnroll], const I (&)[kUnroll],
+                                            const I (&)[kUnroll], const bool (&ok)[kUnroll]) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            if (!kAll && !ok[u]) continue;
+            float xq[kVals];
+            f[u].q.template to_f32<T>(xq);
+            axpy_span<kVals>(f[u].w, xq, s.a);
+        }
+    }
+    __device__ __forceinline__ void merge(State &s, const State &o) { s.merge(o); }
+    __device__ __forceinline__ void to_words(const State &s, uint32_t *w) { s.to_words(w); }
+    __device__ __forceinline__ void from_words(State &s, const uint32_t *w) { s.from_words(w); }
+    __device__ __forceinline__ void row_end(I row, const Row &, State &s, I) {
+        if (L.grp != 0 || !map.live) return;
+        store_span_f32<T, kVpl>(p.out0 + static_cast<int64_t>(row) * p.ldo0, map.off, s.a);
     }
     __device__ __forceinline__ void flush_row(State &) {}
     __device__ __forceinline__ void carry_init(Carry &) {}

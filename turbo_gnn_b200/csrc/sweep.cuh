@@ -21,6 +21,8 @@
 // consumed); only the last, partial batch of a block carries per-edge predicates.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace tgnn {
@@ -74,6 +76,15 @@ __device__ __forceinline__ Lanes make_lanes(int G) {
     return L;
 }
 
+// An op may read a second per-edge stream besides the column index (e.g. the position of the
+// edge in another ordering of the graph): it declares `static constexpr bool kEdgeStream = true`,
+// returns the array from `edge_stream()` and takes the value in `load_edge(col, value, frag)`.
+// The stream is read like the column indices: one coalesced block per 32 edges, prefetched.
+template <class Op, class = void>
+struct has_edge_stream : std::false_type {};
+template <class Op>
+struct has_edge_stream<Op, std::void_t<decltype(Op::kEdgeStream)>> : std::bool_constant<Op::kEdgeStream> {};
+
 // Fold the edges [e0, e1) of one row into `st`; blocks of 32 edges are taken
 // with stride `stride_blocks` starting at block `first_block` (1/0 for a warp
 // that owns the whole row).
@@ -84,19 +95,28 @@ __device__ __forceinline__ void sweep_edges(Op &op, const typename Op::Row &rc, 
                                             const Lanes &L) {
     using I = typename Op::index_t;
     constexpr int U = Op::kUnroll;
+    constexpr bool kStream = has_edge_stream<Op>::value;
     const I step = static_cast<I>(stride_blocks) * 32;
     I base = e0 + static_cast<I>(first_block) * 32;
-    I mine = 0;
-    if (base + L.lane < e1) mine = ld_index(indices + base + L.lane);
+    I mine = 0, smine = 0;
+    const I *stream = nullptr;
+    if constexpr (kStream) stream = op.edge_stream();
+    if (base + L.lane < e1) {
+        mine = ld_index(indices + base + L.lane);
+        if constexpr (kStream) smine = ld_index(stream + base + L.lane);
+    }
     for (; base < e1; base += step) {
         const I nbase = base + step;
-        I next = 0;
-        if (nbase + L.lane < e1) next = ld_index(indices + nbase + L.lane);  // prefetch
+        I next = 0, snext = 0;
+        if (nbase + L.lane < e1) {  // prefetch
+            next = ld_index(indices + nbase + L.lane);
+            if constexpr (kStream) snext = ld_index(stream + nbase + L.lane);
+        }
         const I left = e1 - base;
         const int cnt = left < 32 ? static_cast<int>(left) : 32;
         for (int k = 0; k < cnt; k += L.ngrp * U) {
             typename Op::Frag frag[U];
-            I src[U], eid[U];
+            I src[U], eid[U], sval[U];
             bool ok[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -104,19 +124,31 @@ __device__ __forceinline__ void sweep_edges(Op &op, const typename Op::Row &rc, 
                 ok[u] = slot < cnt;
                 eid[u] = base + slot;
                 src[u] = shfl_idx(mine, slot & 31);
+                if constexpr (kStream) sval[u] = shfl_idx(smine, slot & 31);
             }
             if (k + L.ngrp * U <= cnt) {  // warp-uniform: a full batch needs no per-edge predicate
 #pragma unroll
-                for (int u = 0; u < U; ++u) op.load(src[u], frag[u]);
+                for (int u = 0; u < U; ++u) {
+                    if constexpr (kStream)
+                        op.load_edge(src[u], sval[u], frag[u]);
+                    else
+                        op.load(src[u], frag[u]);
+                }
                 op.template consume<true>(rc, st, frag, src, eid, ok);
             } else {
 #pragma unroll
-                for (int u = 0; u < U; ++u)
-                    if (ok[u]) op.load(src[u], frag[u]);
+                for (int u = 0; u < U; ++u) {
+                    if (!ok[u]) continue;
+                    if constexpr (kStream)
+                        op.load_edge(src[u], sval[u], frag[u]);
+                    else
+                        op.load(src[u], frag[u]);
+                }
                 op.template consume<false>(rc, st, frag, src, eid, ok);
             }
         }
         mine = next;
+        if constexpr (kStream) smine = snext;
     }
 }
 
