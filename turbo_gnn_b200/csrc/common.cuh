@@ -25,8 +25,13 @@
 #ifndef TGNN_MIN_BLOCKS_GT_BWD_SRC
 #define TGNN_MIN_BLOCKS_GT_BWD_SRC(vpl) 4
 #endif
+// The dK pass from handed-over dS gathers one row per edge and does one packed fma per value:
+// 8 edges per batch at 128 registers measured best (7.97 ms against 9.09 with 4 per batch).
 #ifndef TGNN_MIN_BLOCKS_GT_BWD_DK
-#define TGNN_MIN_BLOCKS_GT_BWD_DK(vpl) ((vpl) >= 4 ? 4 : 6)
+#define TGNN_MIN_BLOCKS_GT_BWD_DK(vpl) 4
+#endif
+#ifndef TGNN_GT_DK_UNROLL
+#define TGNN_GT_DK_UNROLL(vpl) ((vpl) >= 4 ? 4 : 8)
 #endif
 #ifndef TGNN_MIN_BLOCKS_GATV2
 #define TGNN_MIN_BLOCKS_GATV2(vpl) ((vpl) >= 4 ? 4 : 5)

@@ -332,7 +332,7 @@ struct GtBwdDkOp : GtBase<T, I, kVpl> {
     using typename B::Params;
     using B::hm; using B::keep; using B::kVals; using B::L; using B::map; using B::p;
     static constexpr int kWords = kVals;
-    static constexpr int kUnroll = 2 * TGNN_ATTN_UNROLL(kVpl);
+    static constexpr int kUnroll = TGNN_GT_DK_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
     static constexpr int kLightMinBlocks = TGNN_MIN_BLOCKS_GT_BWD_DK(kVpl);
     static constexpr int kLightMaxThreads = TGNN_ATTN_LIGHT_THREADS;
