@@ -84,6 +84,8 @@ def test_auto_tiles_rule():
     assert S.auto_tiles(20_000, 20_000, 10_000_000, 2048) == 1
     assert S.auto_tiles(4_194_304, 4_194_304, 65_000_000, 512) == 1
     assert S.auto_tiles(0, 10, 0, 2048) == 1
+    # one gathered 1 KB row per edge on the same graph (238 MB): 4 tiles
+    assert S.auto_tiles(232_965, 232_965, 114_585_574, 1024) == 4
 
 
 def test_tile_table_on_host():

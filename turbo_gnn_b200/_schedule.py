@@ -122,7 +122,7 @@ def auto_tiles(num_rows: int, num_cols: int, num_edges: int, gather_bytes_per_co
         return 1
     footprint = num_cols * gather_bytes_per_col
     mean_degree = num_edges / num_rows
-    if footprint < 2 * L2_BYTES or mean_degree < 2 * TILE_MIN_EDGES_PER_ROW:
+    if 2 * footprint < 3 * L2_BYTES or mean_degree < 2 * TILE_MIN_EDGES_PER_ROW:
         return 1
     tiles = min(round(footprint / TILE_TARGET_BYTES), int(mean_degree // TILE_MIN_EDGES_PER_ROW), MAX_TILES)
     return tiles if tiles >= 2 else 1
