@@ -145,3 +145,33 @@ def test_sharded_ops_at_world_size_one_equal_the_plain_ops():
         ya.sum().backward()
         yb.sum().backward()
         assert rel_err(ya, yb.detach().cpu()) <= 1e-6 and rel_err(xa.grad, xb.grad.cpu()) <= 1e-6
+
+
+def test_calls_can_be_captured_in_a_cuda_graph_and_replayed():
+    """Light + heavy + hub tiers of two ops inside one captured graph (the fork to the library's
+    side stream and the join back are part of the capture); replays follow the inputs."""
+    from helpers import make_graph, random_edges
+    from oracle import scatter_oracle as O
+
+    n = 3000
+    ei = random_edges(n, 20 * n, 77, hubs=3, hub_degree=2500)
+    g = make_graph(ei, n, torch.int32, quantile=0.9)
+    x = torch.randn(n, 64, device="cuda")
+    q, k, v = (torch.randn(n, 2, 32, device="cuda") for _ in range(3))
+    with _C.hub_tier(cta_min_degree=64, hub_min_degree=1024, chunk_edges=256):
+        for _ in range(2):  # warm-up outside the capture: schedules, side stream, caches
+            tg.reduction_aggr(g, x, reduce="sum")
+            tg.graph_transformer_aggr(g, None, q, k, v, 0.2)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            s_out = tg.reduction_aggr(g, x, reduce="sum")
+            a_out = tg.graph_transformer_aggr(g, None, q, k, v, 0.2)
+    for seed in (1, 2):
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        x.copy_(torch.randn(n, 64, device="cuda", generator=gen))
+        q.copy_(torch.randn(n, 2, 32, device="cuda", generator=gen))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert rel_err(s_out, O.segment_reduce(x.cpu(), ei, n, "sum")) <= 1e-5
+        assert rel_err(a_out, O.gt_aggregate(q.cpu(), k.cpu(), v.cpu(), ei, n, 0.2)) <= 1e-5
