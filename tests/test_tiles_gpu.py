@@ -95,3 +95,12 @@ def test_hand_over_falls_back_when_the_second_csr_is_not_the_sorted_transpose():
     r = int(torch.argmax(bp[1:] - bp[:-1]))  # reverse the columns of the longest row
     flipped[bp[r]: bp[r + 1]] = flipped[bp[r]: bp[r + 1]].flip(0)
     assert _C.edge_positions(g.forward_indptr, g.forward_indices, g.backward_indptr, flipped) is None
+
+
+@pytest.mark.parametrize("h,d", [(32, 64), (4, 256)])
+def test_wide_rows_on_feature_slices_with_hand_over_and_tiles(h, d):
+    """Rows wider than one warp's lanes run as feature slices (a slice holds whole heads)."""
+    ei, g = _graph(torch.int32, 0.9, seed=44, n=400)
+    with _C.hub_tier(column_tiles=2):
+        errs = _gt_case(ei, g, h, d, torch.float32, n=400)
+    assert max(errs.values()) <= TOL[torch.float32], errs

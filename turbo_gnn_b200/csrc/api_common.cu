@@ -199,6 +199,7 @@ Geometry make_attn_geometry(int64_t cols, int head_dim, int32_t dtype, int max_v
     Geometry g;
     g.vpl = 1;
     while (g.vpl < max_vpl && g.vpl * 2 <= chunks_per_head && 32 * g.vpl < chunks) g.vpl *= 2;
+    while (g.vpl < 8 && chunks_per_head / g.vpl > 32) g.vpl *= 2;  // a head never spans two warps, whatever the cap
     const int64_t lanes = (chunks + g.vpl - 1) / g.vpl;
     int lanes_per_head = chunks_per_head / g.vpl;
     if (lanes_per_head < 1) lanes_per_head = 1;

@@ -16,7 +16,7 @@ int32_t check_heads(int heads, int head_dim, int64_t cols, int32_t dtype) {
     return TGNN_OK;
 }
 
-// One warp per row: dot[v, h] = <a[v, h, :], b[v, h, :]>.
+// One warp per row (and per feature slice of a very wide row): dot[v, h] = <a[v, h, :], b[v, h, :]>.
 template <typename T, int kVpl>
 __global__ void __launch_bounds__(256) head_dot_kernel(const T *__restrict__ a, int64_t lda, const T *__restrict__ b,
                                                         int64_t ldb, float *__restrict__ dot, int64_t rows, int cols,
@@ -102,8 +102,7 @@ extern "C" int32_t tgnn_head_dot(const tgnn_head_dot_args *a) {
     TGNN_TRY(check_heads(a->heads, a->head_dim, a->a.cols, a->a.dtype));
     TGNN_REQUIRE(a->dot != nullptr || a->a.rows == 0, TGNN_ERR_INVALID_ARGUMENT, "dot is null");
     if (a->a.rows == 0) return TGNN_OK;
-    const Geometry geo = make_attn_geometry(a->a.cols, a->head_dim, a->a.dtype, 8);  // one warp per row, no slices
-    TGNN_REQUIRE(geo.slices == 1, TGNN_ERR_UNSUPPORTED, "rows wider than 256 chunks are not supported here");
+    const Geometry geo = make_attn_geometry(a->a.cols, a->head_dim, a->a.dtype, 8);
     cudaStream_t stream = static_cast<cudaStream_t>(a->exec.stream);
     return dispatch_tiv(a->a.dtype, TGNN_I32, geo.vpl, [&](auto tt, auto, auto vt) -> int32_t {
         using T = typename decltype(tt)::type;
@@ -111,7 +110,8 @@ extern "C" int32_t tgnn_head_dot(const tgnn_head_dot_args *a) {
         int64_t blocks = (a->a.rows + 7) / 8;
         const int64_t cap = static_cast<int64_t>(sm_count(a->exec.device)) * 32;
         if (blocks > cap) blocks = cap;
-        head_dot_kernel<T, kVpl><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        const dim3 grid(static_cast<unsigned>(blocks), geo.slices);  // one warp per row and feature slice
+        head_dot_kernel<T, kVpl><<<grid, 256, 0, stream>>>(
             static_cast<const T *>(a->a.data), a->a.row_stride, static_cast<const T *>(a->b.data), a->b.row_stride,
             a->dot, a->a.rows, static_cast<int>(a->a.cols), a->heads, a->head_dim, geo.G);
         TGNN_CUDA(cudaGetLastError());
