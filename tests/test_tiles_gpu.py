@@ -104,3 +104,9 @@ def test_wide_rows_on_feature_slices_with_hand_over_and_tiles(h, d):
     with _C.hub_tier(column_tiles=2):
         errs = _gt_case(ei, g, h, d, torch.float32, n=400)
     assert max(errs.values()) <= TOL[torch.float32], errs
+
+
+def test_gatv2_wide_rows_on_feature_slices():
+    ei, g = _graph(torch.int32, 0.9, seed=45, n=400)
+    errs = _gatv2_case(ei, g, 32, 64, torch.float32, n=400)
+    assert max(errs.values()) <= TOL[torch.float32], errs

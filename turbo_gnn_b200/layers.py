@@ -20,6 +20,7 @@ from typing import Any, Literal
 import torch
 from torch import nn
 
+from . import _C
 from . import dist as tdist
 from .graph import AdjacencyForwardBackwardWithNodeBuckets
 from .ops import gatv2_aggr, graph_transformer_aggr, reduction_aggr
@@ -64,17 +65,33 @@ class GATv2Conv(nn.Module):
         nn.init.xavier_normal_(self.attn_weights, gain=nn.init.calculate_gain("relu"))
         self.launch = {k: v for k, v in kwargs.items() if k.endswith("_warps")}
 
+    def _padded_projection(self, x: torch.Tensor, dp: int):
+        """Both projections with the head dimension zero-padded to `dp` by padding the (small) weight
+        instead of the `[N, 2 * H * D]` result: the kernels then read the GEMM output in place."""
+        lin = self.left_right_projection
+        w = lin.weight.view(2, self.heads, self.head_dim, -1)
+        w = torch.nn.functional.pad(w, (0, 0, 0, dp - self.head_dim)).reshape(2 * self.heads * dp, -1)
+        b = None
+        if lin.bias is not None:
+            b = torch.nn.functional.pad(lin.bias.view(2, self.heads, self.head_dim), (0, dp - self.head_dim)).reshape(-1)
+        return torch.nn.functional.linear(x, w, b).split(self.heads * dp, -1)
+
     def forward(self, x: torch.Tensor, graph, **kwargs: Any) -> torch.Tensor:
         width = self.heads * self.head_dim
-        x_left, x_right = self.left_right_projection(x).split(width, -1)
-        x_left = x_left.view(-1, self.heads, self.head_dim)
-        x_right = x_right.view(-1, self.heads, self.head_dim)
         attn = self.attn_weights if self.train_attention else self.attn_weights.data
+        dp = _C._padded_head_dim(self.head_dim)
+        if dp != self.head_dim:  # e.g. a 47-wide output head: run the aggregation on 64 columns
+            x_left, x_right = self._padded_projection(x, dp)
+            attn = torch.nn.functional.pad(attn, (0, dp - self.head_dim))
+        else:
+            x_left, x_right = self.left_right_projection(x).split(width, -1)
+        x_left = x_left.view(-1, self.heads, dp)
+        x_right = x_right.view(-1, self.heads, dp)
         if _is_shard(graph):
             out = tdist.sharded_gatv2_aggr(graph, x_left, x_right, attn, self.negative_slope, **self.launch)
         else:
             out = gatv2_aggr(graph, x_left, x_right, attn, self.negative_slope, **self.launch)
-        out = out.reshape(-1, width)
+        out = out[..., : self.head_dim].reshape(-1, width)
         return self._outer_proj(out) if self._outer_proj is not None else out
 
 
