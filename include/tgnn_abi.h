@@ -8,7 +8,9 @@
  *
  *   - The CALLER owns every byte of device memory: inputs, outputs and scratch.
  *     Each op that needs scratch has a `*_workspace_bytes` query; the library
- *     itself never allocates, frees, synchronises the device or calls exit().
+ *     itself never allocates or frees device memory, synchronises the device or
+ *     calls exit().  (It creates one extra stream and two events per device on
+ *     first use, see tgnn_exec.)
  *   - Every call names the device ordinal and the CUDA stream it runs on.
  *   - Every call returns TGNN_OK (0) or a negative tgnn_status; the text of the
  *     last failure on the calling thread is read with tgnn_last_error().  The
