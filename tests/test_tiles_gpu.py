@@ -110,3 +110,11 @@ def test_gatv2_wide_rows_on_feature_slices():
     ei, g = _graph(torch.int32, 0.9, seed=45, n=400)
     errs = _gatv2_case(ei, g, 32, 64, torch.float32, n=400)
     assert max(errs.values()) <= TOL[torch.float32], errs
+
+
+@pytest.mark.parametrize("idt,dt", [(torch.int64, torch.float32), (torch.int32, torch.bfloat16), (torch.int64, torch.float16)])
+def test_hand_over_other_index_and_feature_types(idt, dt):
+    ei, g = _graph(idt, 0.9, seed=46)
+    with _C.hub_tier(column_tiles=2, cta_min_degree=0, hub_min_degree=256, chunk_edges=64):  # every tier in play
+        errs = _gt_case(ei, g, 4, 32, dt)
+    assert max(errs.values()) <= TOL[dt], errs
