@@ -539,8 +539,21 @@ def main_ours(args):
                     h.copy_(o, non_blocking=True)
             cur.wait_stream(side_in)
             grads = job.backward(outs)
-            for h, o in zip(host_out[n_fwd:], grads):
-                h.copy_(o, non_blocking=True)
+            early = ()
+            if job.op == "gt" and job.shard is None:
+                import turbo_gnn_b200 as tg
+
+                ready = tg.gt_source_grads_ready()
+                if ready is not None:  # dQ and dV are complete before the dK pass: they leave while it runs
+                    early = (0, 2)
+                    side_out.wait_event(ready)
+                    with torch.cuda.stream(side_out):
+                        for i in early:
+                            grads[i].record_stream(side_out)
+                            host_out[n_fwd + i].copy_(grads[i], non_blocking=True)
+            for i, o in enumerate(grads):
+                if i not in early:
+                    host_out[n_fwd + i].copy_(o, non_blocking=True)
             cur.wait_stream(side_out)
 
         for _ in range(2):

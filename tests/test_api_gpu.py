@@ -175,3 +175,24 @@ def test_calls_can_be_captured_in_a_cuda_graph_and_replayed():
         torch.cuda.synchronize()
         assert rel_err(s_out, O.segment_reduce(x.cpu(), ei, n, "sum")) <= 1e-5
         assert rel_err(a_out, O.gt_aggregate(q.cpu(), k.cpu(), v.cpu(), ei, n, 0.2)) <= 1e-5
+
+
+def test_event_between_the_graph_transformer_backward_halves():
+    """dQ and dV are final when the event fires, before the dK pass has run."""
+    n = 2000
+    ei = random_edges(n, 30 * n, 78)
+    g = make_graph(ei, n, torch.int32)
+    q, k, v = (torch.randn(n, 4, 32, device="cuda", requires_grad=True) for _ in range(3))
+    out = tg.graph_transformer_aggr(g, None, q, k, v, 0.2)
+    up = torch.randn_like(out)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), up)
+    ev = tg.gt_source_grads_ready()
+    assert ev is not None
+    side = torch.cuda.Stream()
+    side.wait_event(ev)
+    with torch.cuda.stream(side):
+        dq_host = dq.to("cpu", non_blocking=False)
+    ref = [t.detach().double().cpu().requires_grad_() for t in (q, k, v)]
+    want = O.gt_aggregate(*ref, ei, n, 0.2)
+    want.backward(up.double().cpu())
+    assert rel_err(dq_host, ref[0].grad) <= 1e-5 and rel_err(dk, ref[1].grad) <= 1e-5

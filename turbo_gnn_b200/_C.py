@@ -819,6 +819,27 @@ def gt_backward_dk(row_ptr, col_idx, Q, ds, edge_pos, n_rows, light_nodes, heavy
     return _strip(dk, d)
 
 
+# dQ and dV of the graph-transformer backward are complete before the dK pass starts; an event
+# recorded between the two lets a caller move them (e.g. to the host) while dK is computed.
+_source_grads_ready: dict = {}
+
+
+def _mark_source_grads_ready(device: torch.device) -> None:
+    ev = _source_grads_ready.get(device)
+    if ev is None:
+        ev = _source_grads_ready[device] = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(device))
+
+
+def gt_source_grads_ready(device=None):
+    """The CUDA event recorded by the last graph-transformer backward on `device` at the point
+    where dQ and dV were complete (the dK pass follows it), or ``None`` if there was none."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return _source_grads_ready.get(device)
+
+
 class _EdgePositionCache:
     """``edge_positions`` results keyed on the identity of the four CSR arrays."""
 
@@ -906,6 +927,7 @@ def gt_backward_csr_mh(row_ptr, col_idx, row_ptr_T, col_idx_T, Q, K, V, O, dO, l
     ds = torch.empty((col_idx_T.numel(), heads), dtype=torch.float32, device=Q.device)
     dq, dv = gt_backward_src(row_ptr_T, col_idx_T, Q, K, V, dO, lse, delta, scale, light_nodes, heavy_nodes, lw, hw,
                              ds_out=ds)
+    _mark_source_grads_ready(Q.device)
     dk = gt_backward_dk(row_ptr, col_idx, Q, ds, pos, n_rows, fwd_light_nodes, fwd_heavy_nodes, lw, hw)
     return dq, dk, dv
 

@@ -16,6 +16,7 @@ All compute runs in ``libturbo_gnn_b200.so`` (hand-written CUDA for sm_100a, C A
 
 from turbo_gnn_b200._autotune import AutotuneConfig, TunableKernel, TunableParam, with_autotune
 from turbo_gnn_b200._kernels import GATv2AggrKernel, GraphTransformerAggrKernel, ReductionAggrKernel
+from turbo_gnn_b200._C import gt_source_grads_ready
 from turbo_gnn_b200.graph import AdjacencyForwardBackwardWithNodeBuckets
 from turbo_gnn_b200.ops import (
     csr_SPMM_normalized,
@@ -39,4 +40,5 @@ __all__ = [
     "graph_transformer_aggr",
     "spmm_aggr",
     "csr_SPMM_normalized",
+    "gt_source_grads_ready",
 ]
