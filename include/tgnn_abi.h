@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define TGNN_ABI_VERSION 3
+#define TGNN_ABI_VERSION 4
 
 typedef enum tgnn_status {
     TGNN_OK = 0,
@@ -121,6 +121,13 @@ typedef struct tgnn_schedule {
      * tgnn_workspace_bytes(...) + tgnn_tile_workspace_bytes(...) bytes, hub partials first. */
     const void *tile_ptr;
     int32_t num_tiles; /* 0 or 1: untiled */
+    /* A tiled call may be issued in pieces, e.g. while the gathered rows of later column ranges
+     * are still arriving: tile_count > 0 runs only the passes tile_first .. tile_first +
+     * tile_count - 1.  The pieces must be issued in ascending order, with the same arguments and
+     * the same workspace (which carries the parked row states from piece to piece); hub rows
+     * are done by the piece that contains pass 0 and read every column.  0 = all passes. */
+    int32_t tile_first;
+    int32_t tile_count;
     int32_t _pad;
 } tgnn_schedule;
 

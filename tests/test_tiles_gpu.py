@@ -118,3 +118,33 @@ def test_hand_over_other_index_and_feature_types(idt, dt):
     with _C.hub_tier(column_tiles=2, cta_min_degree=0, hub_min_degree=256, chunk_edges=64):  # every tier in play
         errs = _gt_case(ei, g, 4, 32, dt)
     assert max(errs.values()) <= TOL[dt], errs
+
+
+@pytest.mark.parametrize("tiles,chunks", [(4, 3), (5, 8), (1, 2)])
+def test_forward_passes_start_as_source_rows_arrive(tiles, chunks):
+    """Q and V are filled chunk by chunk on another stream; every pass waits only for its rows."""
+    import turbo_gnn_b200 as tg
+    from oracle import scatter_oracle as O
+    from test_attention_gpu import N, _rand
+    from helpers import rel_err
+
+    ei, g = _graph(torch.int32, 0.9, seed=47)
+    q, k, v = (_rand((N, 4, 32), 60 + i) for i in range(3))
+    want = O.gt_aggregate(q.double(), k.double(), v.double(), ei, N, 0.25)
+    hq, hv = q.pin_memory(), v.pin_memory()
+    dq, dv = torch.zeros(N, 4, 32, device="cuda"), torch.zeros(N, 4, 32, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    ready = []
+    with torch.cuda.stream(side):
+        for c in range(chunks):
+            r0, r1 = N * c // chunks, N * (c + 1) // chunks
+            torch.cuda._sleep(2_000_000)  # the rows arrive late on purpose
+            dq[r0:r1].copy_(hq[r0:r1], non_blocking=True)
+            dv[r0:r1].copy_(hv[r0:r1], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(side)
+            ready.append((r1, ev))
+    with _C.hub_tier(column_tiles=tiles, cta_min_degree=1 << 30, hub_min_degree=1 << 30), tg.source_rows_arriving(ready):
+        out = tg.graph_transformer_aggr(g, None, dq, k.cuda(), dv, 0.25)
+    assert rel_err(out, want) <= TOL[torch.float32]

@@ -714,7 +714,33 @@ def gt_forward_csr_mh(row_ptr, col_idx, Q, K, V, scale, light_nodes, heavy_nodes
             workspace=_abi.ptr(ws),
             workspace_bytes=ws_bytes,
         )
-        _abi.call("tgnn_gt_forward", args)
+        ready = _source_rows_ready
+        if not ready:
+            _abi.call("tgnn_gt_forward", args)
+        else:
+            # Q and V are still arriving, in row order: pass t of the column-tiled sweep only reads the
+            # rows of its column range, so it starts as soon as those are there.  Without tiles, or
+            # with hub rows (their pass reads every column), the whole call waits for the last event.
+            stream = torch.cuda.current_stream(q_in.device)
+            tiles, num_src = sched.num_tiles, Q.shape[0]
+            if tiles <= 1 or sched.hub.numel() > 0:
+                for _, ev in ready:
+                    stream.wait_event(ev)
+                _abi.call("tgnn_gt_forward", args)
+            else:
+                span = max((num_src + tiles - 1) // tiles, 1)
+                pending = list(ready)
+                covered = 0
+                for t in range(tiles):
+                    need = min((t + 1) * span, num_src) if t < tiles - 1 else num_src
+                    while covered < need and pending:
+                        rows_done, ev = pending.pop(0)
+                        stream.wait_event(ev)
+                        covered = rows_done
+                    args.sched.tile_first, args.sched.tile_count = t, 1
+                    _abi.call("tgnn_gt_forward", args)
+                for _, ev in pending:
+                    stream.wait_event(ev)
     return _strip(out, d), lse
 
 
@@ -817,6 +843,32 @@ def gt_backward_dk(row_ptr, col_idx, Q, ds, edge_pos, n_rows, light_nodes, heavy
         )
         _abi.call("tgnn_gt_backward_dk", args)
     return _strip(dk, d)
+
+
+# Sources (Q, V rows of `graph_transformer_aggr`) that are still being written when the op is
+# called: a list of (rows_done, event) in ascending row order, "rows [0, rows_done) are valid once
+# the event has fired".  Set through the `source_rows_arriving` context manager.
+_source_rows_ready: list | None = None
+
+
+class source_rows_arriving:
+    """Context manager for a forward call whose Q and V are still being filled in row order (an
+    upload in chunks, a producer kernel on another stream): ``ready`` is a list of
+    ``(rows_done, torch.cuda.Event)``.  The column-tiled sweep starts each pass when the rows of
+    its column range are there; K and the graph must be complete."""
+
+    def __init__(self, ready):
+        self._ready = sorted(ready, key=lambda r: r[0])
+
+    def __enter__(self):
+        global _source_rows_ready
+        self._old, _source_rows_ready = _source_rows_ready, self._ready
+        return self
+
+    def __exit__(self, *exc):
+        global _source_rows_ready
+        _source_rows_ready = self._old
+        return False
 
 
 # dQ and dV of the graph-transformer backward are complete before the dK pass starts; an event

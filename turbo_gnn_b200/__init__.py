@@ -16,7 +16,7 @@ All compute runs in ``libturbo_gnn_b200.so`` (hand-written CUDA for sm_100a, C A
 
 from turbo_gnn_b200._autotune import AutotuneConfig, TunableKernel, TunableParam, with_autotune
 from turbo_gnn_b200._kernels import GATv2AggrKernel, GraphTransformerAggrKernel, ReductionAggrKernel
-from turbo_gnn_b200._C import gt_source_grads_ready
+from turbo_gnn_b200._C import gt_source_grads_ready, source_rows_arriving
 from turbo_gnn_b200.graph import AdjacencyForwardBackwardWithNodeBuckets
 from turbo_gnn_b200.ops import (
     csr_SPMM_normalized,
@@ -41,4 +41,5 @@ __all__ = [
     "spmm_aggr",
     "csr_SPMM_normalized",
     "gt_source_grads_ready",
+    "source_rows_arriving",
 ]

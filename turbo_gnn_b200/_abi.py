@@ -19,7 +19,7 @@ from pathlib import Path
 import torch
 
 LIB_NAME = "libturbo_gnn_b200.so"
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 OK = 0
 F32, F16, BF16 = 0, 1, 2
@@ -67,6 +67,8 @@ class Schedule(C.Structure):
         ("light_warps_per_row", C.c_int32),
         ("tile_ptr", C.c_void_p),
         ("num_tiles", C.c_int32),
+        ("tile_first", C.c_int32),
+        ("tile_count", C.c_int32),
         ("_pad", C.c_int32),
     ]
 
@@ -441,7 +443,7 @@ def _kernels_of(args: C.Structure) -> int:
     sched = getattr(args, "sched", None)
     if sched is None:
         return 1
-    passes = max(int(sched.num_tiles), 1)
+    passes = int(sched.tile_count) if sched.tile_count > 0 else max(int(sched.num_tiles), 1)
     return passes * (int(sched.num_light > 0) + int(sched.num_heavy > 0)) + 2 * int(sched.num_hub > 0)
 
 

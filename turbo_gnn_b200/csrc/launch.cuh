@@ -131,6 +131,13 @@ int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_
                      "scratch must be 256-byte aligned");
     }
     TGNN_REQUIRE(tiles <= 64, TGNN_ERR_LAUNCH_PARAM, "Wrong int value: %d column tiles, at most 64", tiles);
+    int t_begin = 0, t_end = tiles;
+    if (tiles > 1 && s.tile_count > 0) {  // one piece of a tiled call
+        t_begin = s.tile_first;
+        t_end = s.tile_first + s.tile_count;
+        TGNN_REQUIRE(t_begin >= 0 && t_end <= tiles, TGNN_ERR_LAUNCH_PARAM,
+                     "Wrong int value: column tiles %d..%d of %d", t_begin, t_end - 1, tiles);
+    }
     uint32_t *partials = static_cast<uint32_t *>(scratch);
     uint32_t *parked = reinterpret_cast<uint32_t *>(static_cast<unsigned char *>(scratch) + hub_need);
     const I *tile_ptr = static_cast<const I *>(s.tile_ptr);
@@ -155,7 +162,7 @@ int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_
     HubDev<I> hub{static_cast<const I *>(s.hub_rows), s.hub_part_ptr, s.chunk_hub, s.chunk_edges};
     const int hw = s.heavy_warps;
     const size_t merge_smem = static_cast<size_t>(hw > 1 ? hw - 1 : 0) * Op::kWords * 32 * sizeof(uint32_t);
-    if (s.num_hub > 0) {  // hub rows are edge-split already: one untiled pass
+    if (s.num_hub > 0 && t_begin == 0) {  // hub rows are edge-split already: one untiled pass
         dim3 grid(static_cast<unsigned>(s.num_chunks), geo.slices);
         auto k = sweep_heavy_kernel<Op, true>;
         if (merge_smem > 48 * 1024)
@@ -167,7 +174,7 @@ int32_t run_tiers(const typename Op::Params &p, const tgnn_csr &csr, const tgnn_
         TGNN_CUDA(cudaGetLastError());
     }
     HubDev<I> no_hub{nullptr, nullptr, nullptr, 0};
-    for (int t = 0; t < tiles; ++t) {
+    for (int t = t_begin; t < t_end; ++t) {
         const TileDev<I> td = tile_of(t);
         if (s.num_heavy > 0) {
             dim3 grid(static_cast<unsigned>(s.num_heavy), geo.slices);
