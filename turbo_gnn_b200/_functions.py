@@ -49,38 +49,16 @@ class ReductionAggrFunction(torch.autograd.Function):
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(
-        ctx,
-        edge_ptr,
-        edge_idx,
-        X,
-        light,
-        heavy,
-        max_degree,
-        warps_per_block,
-        edges_per_block_heavy_nodes,
-        use_2d_kernel=False,
-        features_per_block=32,
-        tiles_y=8,
-        reduce="min",
+        ctx, edge_ptr, edge_idx, X, light, heavy, max_degree, warps_per_block, edges_per_block_heavy_nodes,
+        use_2d_kernel=False, features_per_block=32, tiles_y=8, reduce="min",
     ):
         if torch.is_autocast_enabled():
             X = X.to(torch.get_autocast_gpu_dtype())
         warps_per_block = _fit_warps_to_features(warps_per_block, X.shape[-1], X.dtype.itemsize)
         needs_grad = ctx.needs_input_grad[2]
         out, arg_idx = _C.reduction_aggr_forward_partitioned(
-            edge_ptr,
-            edge_idx,
-            X,
-            light,
-            heavy,
-            max_degree,
-            warps_per_block,
-            edges_per_block_heavy_nodes,
-            use_2d_kernel,
-            features_per_block,
-            tiles_y,
-            reduce,
-            want_arg=needs_grad,
+            edge_ptr, edge_idx, X, light, heavy, max_degree, warps_per_block, edges_per_block_heavy_nodes,
+            use_2d_kernel, features_per_block, tiles_y, reduce, want_arg=needs_grad,
         )
         ctx.reduce = reduce
         ctx.num_src_nodes = X.size(0)
@@ -112,39 +90,16 @@ class gatv2_function(torch.autograd.Function):
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(
-        ctx,
-        indptr_forward,
-        indices_forward,
-        indptr_backward,
-        indices_backward,
-        x_left,
-        x_right,
-        attention_weights,
-        negative_slope,
-        grad_A_reduce_row_chunk_size,
-        fwd_light_nodes,
-        fwd_heavy_nodes,
-        bwd_light_nodes,
-        bwd_heavy_nodes,
-        forward_light_warps,
-        forward_heavy_warps,
-        backward_light_warps,
-        backward_heavy_warps,
+        ctx, indptr_forward, indices_forward, indptr_backward, indices_backward, x_left, x_right, attention_weights,
+        negative_slope, grad_A_reduce_row_chunk_size, fwd_light_nodes, fwd_heavy_nodes, bwd_light_nodes,
+        bwd_heavy_nodes, forward_light_warps, forward_heavy_warps, backward_light_warps, backward_heavy_warps,
         is_directed,
     ):
         if torch.is_autocast_enabled():
             attention_weights = attention_weights.to(torch.get_autocast_gpu_dtype())
         output, logsumexp = _C.gatv2_forward(
-            x_left,
-            x_right,
-            indptr_forward,
-            indices_forward,
-            attention_weights,
-            negative_slope,
-            fwd_light_nodes,
-            fwd_heavy_nodes,
-            forward_light_warps,
-            forward_heavy_warps,
+            x_left, x_right, indptr_forward, indices_forward, attention_weights, negative_slope, fwd_light_nodes,
+            fwd_heavy_nodes, forward_light_warps, forward_heavy_warps,
         )
         ctx.negative_slope = negative_slope
         ctx.hub_cfg = _C.current_hub_config()
@@ -154,19 +109,8 @@ class gatv2_function(torch.autograd.Function):
         ctx.head_shape = (x_left.shape[1], x_left.shape[2])
         # The output is kept as well: <grad_out, out> per head replaces a neighbour sweep in backward.
         ctx.save_for_backward(
-            x_left,
-            x_right,
-            indptr_forward,
-            indices_forward,
-            indptr_backward,
-            indices_backward,
-            attention_weights,
-            logsumexp,
-            fwd_light_nodes,
-            fwd_heavy_nodes,
-            bwd_light_nodes,
-            bwd_heavy_nodes,
-            output,
+            x_left, x_right, indptr_forward, indices_forward, indptr_backward, indices_backward, attention_weights,
+            logsumexp, fwd_light_nodes, fwd_heavy_nodes, bwd_light_nodes, bwd_heavy_nodes, output,
         )
         return output
 
@@ -193,24 +137,9 @@ class _FusedGraphAttention(torch.autograd.Function):
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(
-        ctx,
-        edge_ptr,
-        edge_idx,
-        edge_ptr_T,
-        edge_idx_T,
-        Q,
-        K,
-        V,
-        scale,
-        fwd_light_nodes,
-        fwd_heavy_nodes,
-        bwd_light_nodes,
-        bwd_heavy_nodes,
-        forward_light_warps,
-        forward_heavy_warps,
-        backward_light_warps,
-        backward_heavy_warps,
-        is_directed,
+        ctx, edge_ptr, edge_idx, edge_ptr_T, edge_idx_T, Q, K, V, scale, fwd_light_nodes, fwd_heavy_nodes,
+        bwd_light_nodes, bwd_heavy_nodes, forward_light_warps, forward_heavy_warps, backward_light_warps,
+        backward_heavy_warps, is_directed,
     ):
         scale = scale or 1 / (Q.shape[-1] ** 0.5)
         out, logsumexp = _C.gt_forward_csr_mh(
@@ -251,14 +180,8 @@ class _CudaSpMMConvFn(torch.autograd.Function):
         ctx.save_for_backward(forward_indptr, forward_indices)
         ctx.cfg = (norm_type, cu_sparse_algorithm_id, block_dim)
         return csr_SPMM_normalized(
-            indptr=forward_indptr,
-            indices=forward_indices,
-            features=x,
-            edge_weights=None,
-            norm=norm_type,
-            algorithm=cu_sparse_algorithm_id,
-            do_transpose_a=False,
-            block_dim=block_dim,
+            indptr=forward_indptr, indices=forward_indices, features=x, edge_weights=None, norm=norm_type,
+            algorithm=cu_sparse_algorithm_id, do_transpose_a=False, block_dim=block_dim,
         )
 
     @staticmethod
@@ -267,27 +190,14 @@ class _CudaSpMMConvFn(torch.autograd.Function):
         forward_indptr, forward_indices = ctx.saved_tensors
         norm_type, alg, block_dim = ctx.cfg
         grad_x = csr_SPMM_normalized(
-            indptr=forward_indptr,
-            indices=forward_indices,
-            features=grad_outputs[0],
-            edge_weights=None,
-            norm=norm_type,
-            algorithm=alg,
-            do_transpose_a=True,
-            block_dim=block_dim,
+            indptr=forward_indptr, indices=forward_indices, features=grad_outputs[0], edge_weights=None,
+            norm=norm_type, algorithm=alg, do_transpose_a=True, block_dim=block_dim,
         )
         return grad_x, None, None, None, None, None
 
 
 def csr_SPMM_normalized(
-    indptr,
-    indices,
-    features,
-    edge_weights=None,
-    norm="none",
-    algorithm=-1,
-    use_cache=True,
-    do_transpose_a=False,
+    indptr, indices, features, edge_weights=None, norm="none", algorithm=-1, use_cache=True, do_transpose_a=False,
     block_dim=256,
 ):
     """``norm(A) @ features`` with norm in none (sum) / right (mean) / left / both (GCN).

@@ -59,18 +59,9 @@ class ReductionAggrKernel(TunableKernel):
 
     def _execute(self, graph, x, **kwargs):
         return ReductionAggrFunction.apply(
-            graph.forward_indptr,
-            graph.forward_indices,
-            x,
-            graph.light_nodes,
-            graph.heavy_nodes,
-            graph.max_degree,
-            self.forward_warps_per_block,
-            self.forward_edges_per_block_heavy_nodes,
-            self.forward_use_2d_kernel,
-            self.forward_features_per_block,
-            self.forward_tiles_y,
-            self.reduce,
+            graph.forward_indptr, graph.forward_indices, x, graph.light_nodes, graph.heavy_nodes, graph.max_degree,
+            self.forward_warps_per_block, self.forward_edges_per_block_heavy_nodes, self.forward_use_2d_kernel,
+            self.forward_features_per_block, self.forward_tiles_y, self.reduce,
         )
 
     def get_tunable_forward_kernel_params(self) -> list[TunableParam]:
@@ -99,24 +90,11 @@ class GATv2AggrKernel(_HubTunables, TunableKernel):
     def _execute(self, graph, x, *, x_neighbors=None, attention_weights=None, negative_slope=None, **kwargs):
         with self._hub():
             return gatv2_function.apply(
-                graph.forward_indptr,
-                graph.forward_indices,
-                graph.backward_indptr,
-                graph.backward_indices,
-                x,
-                x_neighbors,
-                attention_weights,
-                negative_slope,
-                self.backward_grad_A_reduce_row_chunk_size,
-                graph.forward_light_nodes,
-                graph.forward_heavy_nodes,
-                graph.backward_light_nodes,
-                graph.backward_heavy_nodes,
-                self.forward_light_warps,
-                self.forward_heavy_warps,
-                self.backward_light_warps,
-                self.backward_heavy_warps,
-                graph.is_directed,
+                graph.forward_indptr, graph.forward_indices, graph.backward_indptr, graph.backward_indices, x,
+                x_neighbors, attention_weights, negative_slope, self.backward_grad_A_reduce_row_chunk_size,
+                graph.forward_light_nodes, graph.forward_heavy_nodes, graph.backward_light_nodes,
+                graph.backward_heavy_nodes, self.forward_light_warps, self.forward_heavy_warps,
+                self.backward_light_warps, self.backward_heavy_warps, graph.is_directed,
             )
 
     def get_tunable_forward_kernel_params(self) -> list[TunableParam]:
@@ -157,23 +135,10 @@ class GraphTransformerAggrKernel(_HubTunables, TunableKernel):
     def _execute(self, graph, x, *, Q=None, K=None, V=None, scale=None, **kwargs):
         with self._hub():
             return _FusedGraphAttention.apply(
-                graph.forward_indptr,
-                graph.forward_indices,
-                graph.backward_indptr,
-                graph.backward_indices,
-                Q,
-                K,
-                V,
-                scale,
-                graph.forward_light_nodes,
-                graph.forward_heavy_nodes,
-                graph.backward_light_nodes,
-                graph.backward_heavy_nodes,
-                self.forward_light_warps,
-                self.forward_heavy_warps,
-                self.backward_light_warps,
-                self.backward_heavy_warps,
-                graph.is_directed,
+                graph.forward_indptr, graph.forward_indices, graph.backward_indptr, graph.backward_indices, Q, K, V,
+                scale, graph.forward_light_nodes, graph.forward_heavy_nodes, graph.backward_light_nodes,
+                graph.backward_heavy_nodes, self.forward_light_warps, self.forward_heavy_warps,
+                self.backward_light_warps, self.backward_heavy_warps, graph.is_directed,
             )
 
     def get_tunable_forward_kernel_params(self) -> list[TunableParam]:
