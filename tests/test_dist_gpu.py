@@ -36,6 +36,14 @@ def _worker(rank, world, port, out_dir):
         out = tdist.sharded_graph_transformer_aggr(shard, *loc, 0.125, forward_light_warps=1)
         out.backward(shard.local_rows(t["grad"]).contiguous())
         res["gt"] = [out.detach().cpu()] + [x.grad.cpu() for x in loc]
+        # the same with column tiles forced on the shard's sweeps
+        from turbo_gnn_b200 import _C
+
+        loc2 = [shard.local_rows(t[k]).contiguous().requires_grad_() for k in ("Q", "K", "V")]
+        with _C.hub_tier(column_tiles=3):
+            out2 = tdist.sharded_graph_transformer_aggr(shard, *loc2, 0.125, forward_light_warps=1)
+            out2.backward(shard.local_rows(t["grad"]).contiguous())
+        res["gt_tiled"] = [out2.detach().cpu()] + [x.grad.cpu() for x in loc2]
         if rank == 0:
             full = [t[k].clone().requires_grad_() for k in ("Q", "K", "V")]
             ref = tg.graph_transformer_aggr(wl.graph, None, *full, 0.125, forward_light_warps=1)
@@ -86,12 +94,13 @@ def test_two_gpu_shards_match_single_gpu(tmp_path):
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     parts = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(world)]
     ref = parts[0]
-    for key, tol in (("gt", 1e-5), ("gat", 1e-5), ("spmm_none", 2e-2), ("spmm_both", 2e-2)):
-        n_row_tensors = {"gt": 4, "gat": 3}.get(key, 2)
+    for key, tol in (("gt", 1e-5), ("gt_tiled", 1e-5), ("gat", 1e-5), ("spmm_none", 2e-2), ("spmm_both", 2e-2)):
+        n_row_tensors = {"gt": 4, "gt_tiled": 4, "gat": 3}.get(key, 2)
+        want = ref[("gt" if key == "gt_tiled" else key) + "_ref"]
         for i in range(n_row_tensors):
             got = torch.cat([p[key][i] for p in parts])
-            assert got.shape == ref[key + "_ref"][i].shape
-            assert _rel(got, ref[key + "_ref"][i]) <= tol, (key, i)
+            assert got.shape == want[i].shape
+            assert _rel(got, want[i]) <= tol, (key, i)
     # the attention-vector gradient is all-reduced: identical on both ranks, equal to the reference
     assert torch.equal(parts[0]["gat"][3], parts[1]["gat"][3])
     assert _rel(parts[0]["gat"][3], ref["gat_ref"][3]) <= 1e-5
