@@ -95,3 +95,21 @@ def test_bad_norm_raises():
     ei, g = _graph(n=100, seed=12)
     with pytest.raises(RuntimeError):
         tg.spmm_aggr(torch.randn(100, 8).cuda(), g.forward_indptr, g.forward_indices, "sideways", -1, 256)
+
+
+@pytest.mark.parametrize("dt,feat,tol", [(torch.float32, 32, 1e-5), (torch.bfloat16, 64, 2e-2)])
+def test_sum_on_a_graph_with_very_many_rows(dt, feat, tol):
+    """More than 2^18 warp-per-row rows: the launch takes the many-rows build of the weighted sum."""
+    from helpers import make_graph, random_edges, rel_err
+    from oracle import scatter_oracle as O
+    import turbo_gnn_b200 as tg
+
+    n = 300_000
+    ei = random_edges(n, 4 * n, 91, hubs=2, hub_degree=5000)
+    g = make_graph(ei, n, torch.int32)
+    x = torch.randn(n, feat, generator=torch.Generator().manual_seed(5)).to(dt)
+    want = O.segment_reduce(x.float().double(), ei, n, "sum")
+    got = tg.reduction_aggr(g, x.cuda(), warps_per_block=4, reduce="sum")
+    assert rel_err(got.float(), want) <= tol
+    got2 = tg.spmm_aggr(x.cuda(), g.forward_indptr, g.forward_indices, "none", -1, feat)
+    assert rel_err(got2.float(), want) <= tol

@@ -90,6 +90,9 @@ __global__ void norm_scales_kernel(const I *__restrict__ indptr, const int32_t *
     }
 }
 
+// Unweighted sums over this many warp-per-row rows use the many-rows build of WeightedSumOp.
+constexpr int64_t kManyRowsThreshold = 1 << 18;
+
 int grid_for(int64_t work_items, int threads, int device) {
     int64_t blocks = (work_items + threads - 1) / threads;
     const int64_t cap = static_cast<int64_t>(sm_count(device)) * 16;
@@ -143,6 +146,10 @@ extern "C" int32_t tgnn_segment_reduce_forward(const tgnn_segment_reduce_args *a
                 return run_tiers<MinMaxOp<T, I, kVpl, true>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
                                                              a->workspace_bytes, false);
             default:
+                if constexpr (kVpl == 1)
+                    if (a->sched.num_light >= kManyRowsThreshold)
+                        return run_tiers<WeightedSumOp<T, I, 1, false, true>>(p, a->csr, a->sched, a->exec, geo,
+                                                                             a->workspace, a->workspace_bytes, false);
                 return run_tiers<WeightedSumOp<T, I, kVpl, false>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
                                                                    a->workspace_bytes, false);
         }
@@ -230,6 +237,10 @@ extern "C" int32_t tgnn_spmm(const tgnn_spmm_args *a) {
         if (weighted)
             return run_tiers<WeightedSumOp<T, I, kVpl, true>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
                                                               a->workspace_bytes, false);
+        if constexpr (kVpl == 1)
+            if (a->sched.num_light >= kManyRowsThreshold)
+                return run_tiers<WeightedSumOp<T, I, 1, false, true>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
+                                                                     a->workspace_bytes, false);
         return run_tiers<WeightedSumOp<T, I, kVpl, false>>(p, a->csr, a->sched, a->exec, geo, a->workspace,
                                                            a->workspace_bytes, false);
     });

@@ -53,6 +53,9 @@ namespace tgnn {
 // Resident 256-thread CTAs per SM for an op that needs `live_regs` registers of state and
 // fragments (about 28 more go to addresses, indices and loop control).
 constexpr int reduce_min_blocks(int live_regs) {
+#ifdef TGNN_REDUCE_MIN_BLOCKS_OVERRIDE
+    return TGNN_REDUCE_MIN_BLOCKS_OVERRIDE;
+#endif
     return live_regs + 28 <= 64 ? 4 : (live_regs + 28 <= 80 ? 3 : (live_regs + 28 <= 128 ? 2 : 1));
 }
 

@@ -215,7 +215,12 @@ struct MinMaxOp {
 // optional); row result = acc * row_scale[row], or acc / max(degree, 1).
 // The accumulators are float2 pairs folded with the packed fp32 add / fma of sm_100 (one
 // instruction per two features, each half rounded like the scalar instruction).
-template <typename T, typename I, int kVpl, bool kWeighted>
+//
+// kManyRows selects the build for graphs with very many rows: 2 edges per batch and 8 resident
+// CTAs (32 registers).  With millions of mostly short rows the latency of a row's pointer and
+// index loads is hidden by twice as many warps instead of by deeper batches: 7.5 % faster on a
+// 4.2 M-row R-MAT graph, but 35 % slower on a 20 k-row graph, which keeps the default build.
+template <typename T, typename I, int kVpl, bool kWeighted, bool kManyRows = false>
 struct WeightedSumOp {
     using index_t = I;
     using Params = ReduceParams<T, I>;
@@ -223,9 +228,9 @@ struct WeightedSumOp {
     static constexpr int kVals = kVpl * kPer;
     static constexpr int kPairs = kVals / 2;
     static constexpr int kWords = kVals;
-    static constexpr int kUnroll = TGNN_REDUCE_UNROLL(kVpl);
+    static constexpr int kUnroll = kManyRows ? 2 : TGNN_REDUCE_UNROLL(kVpl);
     static constexpr int kCarryWords = 0;
-    static constexpr int kLightMinBlocks = reduce_min_blocks(kWords + kUnroll * (kVpl * 4 + 1));
+    static constexpr int kLightMinBlocks = kManyRows ? 8 : reduce_min_blocks(kWords + kUnroll * (kVpl * 4 + 1));
     static constexpr int kLightMaxThreads = 256;
 
     struct Row {};
